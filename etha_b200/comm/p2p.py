@@ -1,0 +1,243 @@
+"""Peer-to-peer executor: the plan is lowered to a device copy table and run by the sm_100a kernels.
+
+Every producing rank reads its own shard and stores each cell straight into the consumers' strided
+destination slices through peer pointers (no staging bucket, no pack/unpack, no NCCL call); a Replicate
+target is served by one read and a store per replica (or one NVLS multicast store); a Partial source is
+collapsed by the route's primary, which loads the other family members' pending values over NVLink,
+accumulates in fp32 and stores the rounded result directly in the target layout.  Completion is
+published by the last CTA of each producer to a flag on every consumer; consumers wait with a bounded
+acquire-spin kernel, so no host barrier follows the transfer.
+
+Replaces the reference's `bucket_comm` over NCCL (src/etha/comm/comm_methods.py:53-119, src/etha/comm/
+ir.py:229-310, src/etha/comm/transfer.py:20-41).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Sequence
+
+import torch
+
+from .. import ops
+from ..ops.table import CopyTable, DEFAULT_TILE_BYTES
+from ..parallel.peer import PeerMemory, TensorDesc
+from .chunks import cell_slices, chunk_shape_of, padded_slicers
+from .ir import M2MMap, partial_family
+from .planner import mesh_tensor_of, plan_m2m
+
+__all__ = ["PairLayout", "P2PBatch", "TransferTimeout"]
+
+
+class TransferTimeout(RuntimeError):
+    """A consumer gave up waiting for a producer's completion flag."""
+
+
+@dataclass
+class PairLayout:
+    """Source and target layouts of one pair; meshes hold global ranks."""
+
+    source_mesh: Any
+    source_placements: Sequence
+    target_mesh: Any
+    target_placements: Sequence
+    _plan: M2MMap | None = None
+
+    def plan(self) -> M2MMap:
+        if self._plan is None:
+            self._plan = plan_m2m(self.source_mesh, self.source_placements, self.target_mesh, self.target_placements)
+        return self._plan
+
+    @property
+    def source_ranks(self) -> list[int]:
+        return mesh_tensor_of(self.source_mesh).reshape(-1).tolist()
+
+    @property
+    def target_ranks(self) -> list[int]:
+        return mesh_tensor_of(self.target_mesh).reshape(-1).tolist()
+
+
+def _single_process_exchange(obj):
+    return [obj]
+
+
+class P2PBatch:
+    """All tensors of one registration, executed with one table launch per producing rank.
+
+    `exchange(obj) -> list[obj]` is the only collective: it returns every participating rank's object in
+    the order of `ranks` (e.g. `all_gather_object` on a gloo group).  In a single process that plays all
+    ranks, pass several `P2PBatch` objects the same dictionary through `link_local`.
+    """
+
+    def __init__(
+        self,
+        rank: int,
+        ranks: Sequence[int],
+        device: torch.device | int | str,
+        exchange: Callable[[Any], list[Any]] | None = None,
+        peer: PeerMemory | None = None,
+        tile_bytes: int = DEFAULT_TILE_BYTES,
+        use_ipc: bool | None = None,
+    ):
+        self.rank = rank
+        self.ranks = list(ranks)
+        self.device = torch.device(device) if not isinstance(device, torch.device) else device
+        self.exchange = exchange or _single_process_exchange
+        self.peer = peer or PeerMemory(self.device)
+        self.use_ipc = (len(self.ranks) > 1) if use_ipc is None else use_ipc
+        self.tile_bytes = tile_bytes
+        self._entries: list[tuple[PairLayout, torch.Tensor | None, torch.Tensor | None]] = []
+        self.table: CopyTable | None = None
+        self.epoch = 0
+        self._built = False
+
+    def add(self, layout: PairLayout, source: torch.Tensor | None = None, target: torch.Tensor | None = None) -> None:
+        """Register the next tensor of the batch (same order on every rank)."""
+        if self._built:
+            raise RuntimeError("batch already built")
+        self._entries.append((layout, source, target))
+
+    # ---- build (collective) ---------------------------------------------------------------
+    def _describe(self, t: torch.Tensor | None) -> TensorDesc | None:
+        if t is None:
+            return None
+        return self.peer.describe(t) if self.use_ipc else self.peer.describe_local_only(t)
+
+    def build(self) -> "P2PBatch":
+        self._flags = torch.zeros(max(len(self.ranks), 1), dtype=torch.int32, device=self.device)
+        self._status = torch.zeros(2, dtype=torch.int32, device=self.device)
+        mine = {
+            "rank": self.rank,
+            "src": [self._describe(s) for _, s, _ in self._entries],
+            "dst": [self._describe(t) for _, _, t in self._entries],
+            "flags": self._describe(self._flags),
+        }
+        everyone = self.exchange(mine)
+        self._finish_build({e["rank"]: e for e in everyone})
+        return self
+
+    def _finish_build(self, by_rank: dict[int, dict]) -> None:
+        table = CopyTable(self.device, tile_bytes=self.tile_bytes)
+        consumers_i_write: set[int] = set()
+        producers_i_wait: set[int] = set()
+        for i, (layout, src, dst) in enumerate(self._entries):
+            m2m = layout.plan()
+            reductions = list(m2m.source_partial_reductions or [])
+            smesh = mesh_tensor_of(layout.source_mesh)
+            for route in m2m.routes:
+                if not route.dsts:
+                    continue
+                primary = route.src.rank
+                for d in route.dsts:
+                    if d.rank == self.rank:
+                        producers_i_wait.add(primary)
+                if primary != self.rank:
+                    continue
+                sdesc = by_rank[primary]["src"][i]
+                if sdesc is None:
+                    raise ValueError(f"rank {primary} registered no source for tensor {i}")
+                s_slicers = padded_slicers(m2m.source_num_slicers, len(sdesc.shape))
+                s_cshape = chunk_shape_of(sdesc.shape, s_slicers)
+                s_index = cell_slices(route.src.cell, s_cshape, len(sdesc.shape))
+                fam = partial_family(smesh, reductions, primary) if reductions else None
+                members = fam.ranks if fam is not None else (primary,)
+                srcs = []
+                for q in members:
+                    qdesc = by_rank[q]["src"][i]
+                    if qdesc is None or tuple(qdesc.shape) != tuple(sdesc.shape):
+                        raise ValueError(f"Partial contributor {q} of tensor {i} has no matching shard")
+                    srcs.append(self.peer.slice_ref(qdesc, s_index))
+                dsts = []
+                for d in route.dsts:
+                    ddesc = by_rank[d.rank]["dst"][i]
+                    if ddesc is None:
+                        raise ValueError(f"rank {d.rank} registered no target for tensor {i}")
+                    t_slicers = padded_slicers(m2m.target_num_slicers, len(ddesc.shape))
+                    t_cshape = chunk_shape_of(ddesc.shape, t_slicers)
+                    if tuple(t_cshape) != tuple(s_cshape):
+                        raise ValueError(f"tensor {i}: cell shapes differ, source {s_cshape} vs target {t_cshape} on rank {d.rank}")
+                    dsts.append(self.peer.slice_ref(ddesc, cell_slices(d.cell, t_cshape, len(ddesc.shape))))
+                    consumers_i_write.add(d.rank)
+                table.add(s_cshape, srcs, dsts, fam.sizes if fam else (), fam.ops if fam else ())
+        table.finalize()
+        self.table = table
+        # flags: slot k of a consumer's flag array belongs to producer ranks[k]
+        my_slot = self.ranks.index(self.rank)
+        addrs = []
+        for c in sorted(consumers_i_write):
+            fref = self.peer.slice_ref(by_rank[c]["flags"])
+            addrs.append(fref.ptr + 4 * my_slot)
+        self._signals = torch.tensor(addrs, dtype=torch.int64, device=self.device) if addrs else None
+        self._consumers = sorted(consumers_i_write)
+        self._producers = sorted(producers_i_wait)
+        self._wait_slots = (
+            torch.tensor([self.ranks.index(p) for p in self._producers], dtype=torch.int32, device=self.device)
+            if self._producers else None
+        )
+        self._built = True
+
+    # ---- execution -----------------------------------------------------------------------
+    @property
+    def is_producer(self) -> bool:
+        return self.table is not None and (not self.table.empty or bool(self._consumers))
+
+    @property
+    def is_consumer(self) -> bool:
+        return bool(self._producers)
+
+    def begin(self) -> int:
+        """Advance to the next transfer epoch (every rank calls it once per transfer)."""
+        self.epoch += 1
+        return self.epoch
+
+    def send(self, stream: torch.cuda.Stream | None = None, ctas_per_sm: int = 2, bulk: bool = False) -> None:
+        """Enqueue this rank's copies and the completion signal. Call `begin()` first."""
+        if self.table is None:
+            raise RuntimeError("build() first")
+        if self._signals is None and self.table.empty:
+            return
+        self.table.launch(stream, self._signals, self.epoch, ctas_per_sm=ctas_per_sm, bulk=bulk)
+
+    def recv(self, stream: torch.cuda.Stream | None = None, timeout_s: float = 10.0) -> None:
+        """Enqueue the bounded wait for every producer that writes into this rank."""
+        if self._wait_slots is None:
+            return
+        ops.wait_flags(self._flags, self._wait_slots, self.epoch, self._status, timeout_s, stream)
+
+    def check(self) -> None:
+        """After a stream synchronize: raise if the wait timed out or a kernel reported a bad op."""
+        if self._wait_slots is not None:
+            st = self._status.tolist()
+            if st[0] == ops.STATUS_TIMEOUT:
+                who = self._producers[st[1]] if 0 <= st[1] < len(self._producers) else st[1]
+                raise TransferTimeout(f"rank {self.rank}: no completion flag from producer rank {who} (epoch {self.epoch})")
+        if self.table is not None and not self.table.empty and self.table.error_word() != 0:
+            raise RuntimeError(f"rank {self.rank}: copy kernel reported error {self.table.error_word()}")
+
+    def transfer(self, stream: torch.cuda.Stream | None = None, timeout_s: float = 10.0, **kw) -> None:
+        """begin + send + recv for ranks that may hold either or both roles."""
+        self.begin()
+        self.send(stream, **kw)
+        self.recv(stream, timeout_s)
+
+    @property
+    def payload_bytes(self) -> int:
+        return self.table.payload_bytes if self.table is not None else 0
+
+
+def link_local(batches: Sequence[P2PBatch]) -> None:
+    """Build several logical ranks that live in ONE process (tests, 1-GPU runs): no IPC, no collective."""
+    gathered = []
+    for b in batches:
+        b.use_ipc = False
+        b._flags = torch.zeros(max(len(b.ranks), 1), dtype=torch.int32, device=b.device)
+        b._status = torch.zeros(2, dtype=torch.int32, device=b.device)
+        gathered.append({
+            "rank": b.rank,
+            "src": [b._describe(s) for _, s, _ in b._entries],
+            "dst": [b._describe(t) for _, _, t in b._entries],
+            "flags": b._describe(b._flags),
+        })
+    by_rank = {e["rank"]: e for e in gathered}
+    for b in batches:
+        b._finish_build(by_rank)

@@ -1,0 +1,19 @@
+"""Weight-shape catalogs of the model families used by the benchmarks and examples."""
+
+from .catalog import (
+    LayoutRule,
+    ModelSpec,
+    TensorSpec,
+    fsdp_layout,
+    llama3_8b,
+    mixtral_8x7b,
+    qwen2_7b,
+    qwen3_0p6b,
+    tiny_llama,
+    vllm_tp_layout,
+)
+
+__all__ = [
+    "ModelSpec", "TensorSpec", "LayoutRule", "llama3_8b", "qwen2_7b", "mixtral_8x7b", "qwen3_0p6b", "tiny_llama",
+    "fsdp_layout", "vllm_tp_layout",
+]

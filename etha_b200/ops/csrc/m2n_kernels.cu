@@ -1,0 +1,506 @@
+// sm_100a kernels of the M-to-N redistribution: strided gather -> (convert | reduce) -> strided
+// scatter into local, peer or multicast memory, plus the release/acquire flag kernels.
+//
+// One persistent launch walks a device-resident table of `M2NOp`s (see m2n.h).  The table is built
+// once per registered batch and launched once per transfer, so a transfer costs no host work per
+// chunk and no staging buffer: the producer GPU reads its own memory and stores straight into the
+// consumers' slices over NVLink.  This replaces the reference's per-chunk slice/contiguous/cast/
+// pack kernels and its NCCL send/recv/broadcast/all-reduce calls (src/etha/comm/ir.py:101-141,
+// 229-310; src/etha/comm/transfer.py:20-41).
+#include "m2n.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <type_traits>
+
+#include "common.h"
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// memory access helpers
+// ---------------------------------------------------------------------------------------------
+template <typename V>
+__device__ __forceinline__ V ld_stream(const void* p);
+
+template <>
+__device__ __forceinline__ uint4 ld_stream<uint4>(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+template <>
+__device__ __forceinline__ uint2 ld_stream<uint2>(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+template <>
+__device__ __forceinline__ uint32_t ld_stream<uint32_t>(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+template <>
+__device__ __forceinline__ uint16_t ld_stream<uint16_t>(const void* p) {
+  uint16_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+  return v;
+}
+template <>
+__device__ __forceinline__ uint8_t ld_stream<uint8_t>(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u8 %0, [%1];" : "=r"(v) : "l"(p));
+  return (uint8_t)v;
+}
+
+template <typename V>
+__device__ __forceinline__ void st_plain(void* p, V v) {
+  *reinterpret_cast<V*>(p) = v;
+}
+
+// one 16-byte store delivered by NVSwitch to every GPU bound to the multicast object
+__device__ __forceinline__ void st_multimem16(void* p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t mul, uint32_t shr) {
+  return mul ? (__umulhi(n, mul) >> shr) : n;  // mul == 0 encodes "divide by one"
+}
+
+// byte offsets of unit `unit` of the op inside the source and the destination box
+template <int ND = -1>
+__device__ __forceinline__ void unit_offsets(const M2NOp& op, uint32_t unit, int64_t& so, int64_t& dof) {
+  if constexpr (ND == 0) {  // one contiguous run on both sides
+    so = (int64_t)unit * op.unit_bytes_src;
+    dof = (int64_t)unit * op.unit_bytes_dst;
+    return;
+  }
+  uint32_t q = fast_div(unit, op.div_mul[M2N_MAX_DIMS], op.div_shr[M2N_MAX_DIMS]);
+  uint32_t col = unit - q * op.inner_units;
+  so = (int64_t)col * op.unit_bytes_src;
+  dof = (int64_t)col * op.unit_bytes_dst;
+  if constexpr (ND == 1) {  // rows of a matrix
+    so += (int64_t)q * op.src_stride[0];
+    dof += (int64_t)q * op.dst_stride[0];
+    return;
+  }
+  const int nd = op.ndim;
+#pragma unroll
+  for (int d = M2N_MAX_DIMS - 1; d >= 0; --d) {
+    if (d < nd) {
+      uint32_t q2 = (d == 0) ? 0u : fast_div(q, op.div_mul[d], op.div_shr[d]);
+      uint32_t i = q - q2 * op.extent[d];
+      so += (int64_t)i * op.src_stride[d];
+      dof += (int64_t)i * op.dst_stride[d];
+      q = q2;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// typed element vectors (8 elements) for conversion and reduction
+// ---------------------------------------------------------------------------------------------
+template <int DT>
+struct Elem;
+
+template <>
+struct Elem<M2N_F32> {
+  static __device__ __forceinline__ void load8(const char* p, float (&f)[8]) {
+    uint4 a = ld_stream<uint4>(p), b = ld_stream<uint4>(p + 16);
+    f[0] = __uint_as_float(a.x), f[1] = __uint_as_float(a.y), f[2] = __uint_as_float(a.z), f[3] = __uint_as_float(a.w);
+    f[4] = __uint_as_float(b.x), f[5] = __uint_as_float(b.y), f[6] = __uint_as_float(b.z), f[7] = __uint_as_float(b.w);
+  }
+  static __device__ __forceinline__ void store8(char* p, const float (&f)[8]) {
+    st_plain<uint4>(p, make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3])));
+    st_plain<uint4>(p + 16, make_uint4(__float_as_uint(f[4]), __float_as_uint(f[5]), __float_as_uint(f[6]), __float_as_uint(f[7])));
+  }
+  static __device__ __forceinline__ float load1(const char* p) { return __uint_as_float(ld_stream<uint32_t>(p)); }
+  static __device__ __forceinline__ void store1(char* p, float f) { *reinterpret_cast<float*>(p) = f; }
+};
+
+template <>
+struct Elem<M2N_BF16> {
+  static __device__ __forceinline__ float up(uint32_t w, int hi) { return __uint_as_float(hi ? (w & 0xffff0000u) : (w << 16)); }
+  static __device__ __forceinline__ void load8(const char* p, float (&f)[8]) {
+    uint4 a = ld_stream<uint4>(p);
+    f[0] = up(a.x, 0), f[1] = up(a.x, 1), f[2] = up(a.y, 0), f[3] = up(a.y, 1);
+    f[4] = up(a.z, 0), f[5] = up(a.z, 1), f[6] = up(a.w, 0), f[7] = up(a.w, 1);
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  static __device__ __forceinline__ void store8(char* p, const float (&f)[8]) {
+    st_plain<uint4>(p, make_uint4(pack(f[0], f[1]), pack(f[2], f[3]), pack(f[4], f[5]), pack(f[6], f[7])));
+  }
+  static __device__ __forceinline__ float load1(const char* p) { return __uint_as_float((uint32_t)ld_stream<uint16_t>(p) << 16); }
+  static __device__ __forceinline__ void store1(char* p, float f) { *reinterpret_cast<__nv_bfloat16*>(p) = __float2bfloat16_rn(f); }
+};
+
+template <>
+struct Elem<M2N_F16> {
+  static __device__ __forceinline__ void unpack(uint32_t w, float& lo, float& hi) {
+    __half2 h = *reinterpret_cast<__half2*>(&w);
+    float2 f = __half22float2(h);
+    lo = f.x, hi = f.y;
+  }
+  static __device__ __forceinline__ void load8(const char* p, float (&f)[8]) {
+    uint4 a = ld_stream<uint4>(p);
+    unpack(a.x, f[0], f[1]), unpack(a.y, f[2], f[3]), unpack(a.z, f[4], f[5]), unpack(a.w, f[6], f[7]);
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  static __device__ __forceinline__ void store8(char* p, const float (&f)[8]) {
+    st_plain<uint4>(p, make_uint4(pack(f[0], f[1]), pack(f[2], f[3]), pack(f[4], f[5]), pack(f[6], f[7])));
+  }
+  static __device__ __forceinline__ float load1(const char* p) {
+    uint16_t b = ld_stream<uint16_t>(p);
+    return __half2float(*reinterpret_cast<__half*>(&b));
+  }
+  static __device__ __forceinline__ void store1(char* p, float f) { *reinterpret_cast<__half*>(p) = __float2half_rn(f); }
+};
+
+__device__ __forceinline__ float reduce2(float a, float b, int op) {
+  switch (op) {
+    case M2N_MAX: return (a != a) ? a : ((b != b) ? b : fmaxf(a, b));  // NaN propagates, like torch.maximum
+    case M2N_MIN: return (a != a) ? a : ((b != b) ? b : fminf(a, b));
+    case M2N_PROD: return a * b;
+    default: return a + b;  // SUM and AVG
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// tile bodies
+// ---------------------------------------------------------------------------------------------
+template <typename V, int UNROLL, int ND>
+__device__ __forceinline__ void tile_raw(const M2NOp& op, uint32_t base, uint32_t limit) {
+  V v[UNROLL];
+  int64_t doff[UNROLL];
+  bool ok[UNROLL];
+  const char* src = reinterpret_cast<const char*>(op.src[0]);
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    uint32_t unit = base + u * blockDim.x + threadIdx.x;
+    ok[u] = unit < limit;
+    if (ok[u]) {
+      int64_t so;
+      unit_offsets<ND>(op, unit, so, doff[u]);
+      v[u] = ld_stream<V>(src + so);
+    }
+  }
+  const int nd = op.ndst;
+  if constexpr (std::is_same<V, uint4>::value) {
+    if (op.flags & M2N_FLAG_MULTIMEM) {
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u)
+        if (ok[u]) st_multimem16(reinterpret_cast<char*>(op.dst[0]) + doff[u], v[u]);
+      return;
+    }
+  }
+  for (int j = 0; j < nd; ++j) {
+    char* dst = reinterpret_cast<char*>(op.dst[j]);
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+      if (ok[u]) st_plain<V>(dst + doff[u], v[u]);
+  }
+}
+
+template <int SDT, int DDT, int UNROLL>
+__device__ __forceinline__ void tile_cvt8(const M2NOp& op, uint32_t base, uint32_t limit) {
+  const char* src = reinterpret_cast<const char*>(op.src[0]);
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    uint32_t unit = base + u * blockDim.x + threadIdx.x;
+    if (unit < limit) {
+      int64_t so, dof;
+      unit_offsets(op, unit, so, dof);
+      float f[8];
+      Elem<SDT>::load8(src + so, f);
+      for (int j = 0; j < op.ndst; ++j) Elem<DDT>::store8(reinterpret_cast<char*>(op.dst[j]) + dof, f);
+    }
+  }
+}
+
+template <int SDT, int DDT, int UNROLL>
+__device__ __forceinline__ void tile_cvt1(const M2NOp& op, uint32_t base, uint32_t limit) {
+  const char* src = reinterpret_cast<const char*>(op.src[0]);
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    uint32_t unit = base + u * blockDim.x + threadIdx.x;
+    if (unit < limit) {
+      int64_t so, dof;
+      unit_offsets(op, unit, so, dof);
+      float f = Elem<SDT>::load1(src + so);
+      for (int j = 0; j < op.ndst; ++j) Elem<DDT>::store1(reinterpret_cast<char*>(op.dst[j]) + dof, f);
+    }
+  }
+}
+
+// Partial collapse: level 0 groups of red_size[0] consecutive sources, then level 1 over the group results;
+// fp32 accumulation in ascending source order, "avg" divides by the group size, one rounding at the store.
+template <int SDT, int DDT, int N>
+__device__ __forceinline__ void tile_reduce(const M2NOp& op, uint32_t base, uint32_t limit, int unroll) {
+  const int s0 = op.red_size[0], s1 = op.red_size[1];
+  const int op0 = op.red_op[0], op1 = op.red_op[1];
+  for (int u = 0; u < unroll; ++u) {
+    uint32_t unit = base + u * blockDim.x + threadIdx.x;
+    if (unit >= limit) continue;
+    int64_t so, dof;
+    unit_offsets(op, unit, so, dof);
+    float acc[N];
+    for (int g = 0; g < s1; ++g) {
+      float a[N];
+      for (int i = 0; i < s0; ++i) {
+        const char* p = reinterpret_cast<const char*>(op.src[g * s0 + i]) + so;
+        float f[N];
+        if constexpr (N == 8) {
+          Elem<SDT>::load8(p, f);
+        } else {
+          f[0] = Elem<SDT>::load1(p);
+        }
+#pragma unroll
+        for (int k = 0; k < N; ++k) a[k] = (i == 0) ? f[k] : reduce2(a[k], f[k], op0);
+      }
+      if (op0 == M2N_AVG) {
+#pragma unroll
+        for (int k = 0; k < N; ++k) a[k] = __fdiv_rn(a[k], (float)s0);
+      }
+#pragma unroll
+      for (int k = 0; k < N; ++k) acc[k] = (g == 0) ? a[k] : reduce2(acc[k], a[k], op1);
+    }
+    if (op1 == M2N_AVG && s1 > 1) {
+#pragma unroll
+      for (int k = 0; k < N; ++k) acc[k] = __fdiv_rn(acc[k], (float)s1);
+    }
+    for (int j = 0; j < op.ndst; ++j) {
+      char* d = reinterpret_cast<char*>(op.dst[j]) + dof;
+      if constexpr (N == 8) {
+        Elem<DDT>::store8(d, acc);
+      } else {
+        Elem<DDT>::store1(d, acc[0]);
+      }
+    }
+  }
+}
+
+template <int UNROLL>
+__device__ __forceinline__ bool dispatch_typed(const M2NOp& op, uint32_t base, uint32_t limit) {
+  const int key = (op.mode << 8) | (op.src_dtype << 4) | op.dst_dtype;
+  const bool vec = op.unit_elems == 8;
+#define CASE_CVT(S, D)                                                   \
+  case (M2N_MODE_CVT << 8) | (S << 4) | D:                               \
+    if (vec) tile_cvt8<S, D, UNROLL>(op, base, limit);                   \
+    else tile_cvt1<S, D, UNROLL>(op, base, limit);                       \
+    return true;
+#define CASE_RED(S, D)                                                   \
+  case (M2N_MODE_REDUCE << 8) | (S << 4) | D:                            \
+    if (vec) tile_reduce<S, D, 8>(op, base, limit, UNROLL);              \
+    else tile_reduce<S, D, 1>(op, base, limit, UNROLL);                  \
+    return true;
+  switch (key) {
+    CASE_CVT(M2N_F32, M2N_BF16) CASE_CVT(M2N_F32, M2N_F16) CASE_CVT(M2N_BF16, M2N_F32) CASE_CVT(M2N_F16, M2N_F32)
+    CASE_CVT(M2N_BF16, M2N_F16) CASE_CVT(M2N_F16, M2N_BF16)
+    CASE_RED(M2N_F32, M2N_F32) CASE_RED(M2N_F32, M2N_BF16) CASE_RED(M2N_F32, M2N_F16) CASE_RED(M2N_BF16, M2N_BF16)
+    CASE_RED(M2N_BF16, M2N_F32) CASE_RED(M2N_BF16, M2N_F16) CASE_RED(M2N_F16, M2N_F16) CASE_RED(M2N_F16, M2N_F32)
+    CASE_RED(M2N_F16, M2N_BF16)
+    default: return false;
+  }
+#undef CASE_CVT
+#undef CASE_RED
+}
+
+// after the last CTA: publish `epoch` to every flag with system-scope release ordering
+__device__ __forceinline__ void finish_and_signal(uint32_t* sync, const uint64_t* signals, uint32_t n_signals,
+                                                  uint32_t epoch) {
+  __shared__ uint32_t s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    uint32_t prev = atomicAdd(&sync[0], 1u);
+    s_last = (prev == gridDim.x - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x == 0) sync[0] = 0;  // ready for the next launch on this stream
+    __threadfence_system();
+    for (uint32_t i = threadIdx.x; i < n_signals; i += blockDim.x) {
+      uint32_t* flag = reinterpret_cast<uint32_t*>(signals[i]);
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+    }
+  }
+}
+
+constexpr int kUnroll = 4;
+
+// binary search of the op that owns `tile`, and (re)load of that op into shared memory
+__device__ __forceinline__ uint32_t locate_op(const M2NOp* __restrict__ ops, const uint32_t* __restrict__ tile_start,
+                                              uint32_t n_ops, uint32_t tile, uint32_t& cur, M2NOp* s_op) {
+  uint32_t lo = 0, hi = n_ops;
+  while (hi - lo > 1) {
+    uint32_t mid = (lo + hi) >> 1;
+    if (tile_start[mid] <= tile) lo = mid; else hi = mid;
+  }
+  if (lo != cur) {
+    __syncthreads();
+    const uint4* g = reinterpret_cast<const uint4*>(ops + lo);
+    uint4* s = reinterpret_cast<uint4*>(s_op);
+    for (uint32_t i = threadIdx.x; i < sizeof(M2NOp) / 16; i += blockDim.x) s[i] = g[i];
+    __syncthreads();
+    cur = lo;
+  }
+  return lo;
+}
+
+// Fast class: 16-byte bit copies whose box is one run or rows of a matrix (the bulk of a weight sync).
+__global__ void __launch_bounds__(512, 2)
+m2n_fast_kernel(const M2NOp* __restrict__ ops, const uint32_t* __restrict__ tile_start, uint32_t n_ops, uint32_t* sync,
+                const uint64_t* __restrict__ signals, uint32_t n_signals, uint32_t epoch, int do_signal) {
+  __shared__ M2NOp s_op;
+  const uint32_t total_tiles = n_ops ? tile_start[n_ops] : 0;
+  uint32_t cur = 0xffffffffu;
+  for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    const uint32_t lo = locate_op(ops, tile_start, n_ops, tile, cur, &s_op);
+    const M2NOp& op = s_op;
+    const uint32_t base = (tile - tile_start[lo]) * op.tile_units;
+    const uint32_t limit = min(op.total_units, base + op.tile_units);
+    const uint32_t step = blockDim.x * kUnroll;
+    if (op.ndim == 0) {
+      for (uint32_t b = base; b < limit; b += step) tile_raw<uint4, kUnroll, 0>(op, b, limit);
+    } else {
+      for (uint32_t b = base; b < limit; b += step) tile_raw<uint4, kUnroll, 1>(op, b, limit);
+    }
+  }
+  if (do_signal) finish_and_signal(sync, signals, n_signals, epoch);
+}
+
+// General class: any other bit copy, converting copies and Partial collapses.
+constexpr int kGenUnroll = 2;
+template <typename V>
+__device__ __noinline__ void walk_raw(const M2NOp& op, uint32_t base, uint32_t limit) {
+  for (uint32_t b = base; b < limit; b += blockDim.x * kGenUnroll) tile_raw<V, kGenUnroll, -1>(op, b, limit);
+}
+__device__ __noinline__ bool walk_typed(const M2NOp& op, uint32_t base, uint32_t limit) {
+  for (uint32_t b = base; b < limit; b += blockDim.x * kGenUnroll)
+    if (!dispatch_typed<kGenUnroll>(op, b, limit)) return false;
+  return true;
+}
+
+__global__ void __launch_bounds__(256, 2)
+m2n_general_kernel(const M2NOp* __restrict__ ops, const uint32_t* __restrict__ tile_start, uint32_t n_ops,
+                   uint32_t* sync, const uint64_t* __restrict__ signals, uint32_t n_signals, uint32_t epoch,
+                   int do_signal) {
+  __shared__ M2NOp s_op;
+  const uint32_t total_tiles = n_ops ? tile_start[n_ops] : 0;
+  uint32_t cur = 0xffffffffu;
+  for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    const uint32_t lo = locate_op(ops, tile_start, n_ops, tile, cur, &s_op);
+    const M2NOp& op = s_op;
+    const uint32_t base = (tile - tile_start[lo]) * op.tile_units;
+    const uint32_t limit = min(op.total_units, base + op.tile_units);
+    if (op.mode == M2N_MODE_RAW) {
+      switch (op.unit_bytes_src) {
+        case 16: walk_raw<uint4>(op, base, limit); break;
+        case 8: walk_raw<uint2>(op, base, limit); break;
+        case 4: walk_raw<uint32_t>(op, base, limit); break;
+        case 2: walk_raw<uint16_t>(op, base, limit); break;
+        default: walk_raw<uint8_t>(op, base, limit); break;
+      }
+    } else if (!walk_typed(op, base, limit)) {
+      if (threadIdx.x == 0) sync[1] = M2N_BAD_OP;
+    }
+  }
+  if (do_signal) finish_and_signal(sync, signals, n_signals, epoch);
+}
+
+__global__ void set_flags_kernel(const uint64_t* __restrict__ signals, uint32_t n_signals, uint32_t epoch) {
+  __threadfence_system();
+  for (uint32_t i = threadIdx.x; i < n_signals; i += blockDim.x) {
+    uint32_t* flag = reinterpret_cast<uint32_t*>(signals[i]);
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+  }
+}
+
+// Bounded acquire-wait.  A flag counts as set once it reached `epoch` (wrap-safe compare).  On timeout the
+// kernel reports which flag was missing and returns; it never traps and never spins without a limit.
+__global__ void wait_flags_kernel(const uint32_t* __restrict__ flags, const uint32_t* __restrict__ which, uint32_t n,
+                                  uint32_t epoch, uint64_t timeout_ns, uint32_t* status) {
+  __shared__ uint32_t s_fail, s_who;
+  if (threadIdx.x == 0) { s_fail = 0; s_who = 0xffffffffu; }
+  __syncthreads();
+  for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+    const uint32_t* flag = flags + which[i];
+    uint64_t t0;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    bool ok = false;
+    for (uint64_t it = 0; it < (1ull << 34); ++it) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if ((int32_t)(v - epoch) >= 0) { ok = true; break; }
+      if ((it & 63) == 63) {
+        uint64_t t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        if (t - t0 > timeout_ns) break;
+        __nanosleep(200);
+      }
+    }
+    if (!ok) { atomicExch(&s_fail, 1u); atomicMin(&s_who, i); }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    status[1] = s_who;
+    __threadfence_system();
+    status[0] = s_fail ? M2N_TIMEOUT : M2N_OK;
+  }
+}
+
+inline int fail(cudaError_t e, const char* what) {
+  snprintf(etha_err_buf(), ETHA_ERR_LEN, "%s: %s", what, cudaGetErrorString(e));
+  return -(int)e - 1000;
+}
+
+}  // namespace
+
+extern "C" {
+
+int etha_m2n_launch(const M2NOp* ops, const uint32_t* tile_start, uint32_t n_ops, int typed, int grid, int block,
+                    uint32_t* sync_scratch, const uint64_t* signals, uint32_t n_signals, uint32_t epoch,
+                    int do_signal, void* stream) {
+  if (grid < 1) grid = 1;
+  if (typed) {
+    if (block < 32 || block > 256 || (block & 31)) block = 256;
+    m2n_general_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(ops, tile_start, n_ops, sync_scratch, signals, n_signals,
+                                                               epoch, do_signal);
+  } else {
+    if (block < 32 || block > 512 || (block & 31)) block = 512;
+    m2n_fast_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(ops, tile_start, n_ops, sync_scratch, signals, n_signals,
+                                                             epoch, do_signal);
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : fail(e, "m2n kernel launch");
+}
+
+int etha_set_flags(const uint64_t* signals, uint32_t n_signals, uint32_t epoch, void* stream) {
+  set_flags_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(signals, n_signals, epoch);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : fail(e, "set_flags launch");
+}
+
+int etha_wait_flags(const uint32_t* flags, const uint32_t* which, uint32_t n, uint32_t epoch, uint64_t timeout_ns,
+                    uint32_t* status, void* stream) {
+  int block = n < 32 ? 32 : (n > 256 ? 256 : (int)((n + 31) & ~31u));
+  wait_flags_kernel<<<1, block, 0, (cudaStream_t)stream>>>(flags, which, n, epoch, timeout_ns, status);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : fail(e, "wait_flags launch");
+}
+
+}  // extern "C"

@@ -1,0 +1,216 @@
+"""Device-resident copy table: built once per registered batch, launched once per transfer.
+
+`CopyTable.add*` collect strided-box copies (optionally converting, fanning out to several
+destinations or collapsing several Partial sources); `finalize()` packs them with the native packer,
+splits them into the two kernel classes and uploads them; `launch()` issues at most two persistent
+kernels on the given stream and, when asked, publishes an epoch to the consumers' flags from the
+last CTA.  Nothing here allocates or touches the host during `launch()`.
+
+The reference does this work per chunk and per transfer in Python (`Chunk.prepare`/`Bucket.prepare`/
+`finalize`, src/etha/comm/ir.py:101-141,229-310).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from . import lib as L
+
+_DT_CODE = {torch.float32: L.DT_F32, torch.bfloat16: L.DT_BF16, torch.float16: L.DT_F16}
+
+DEFAULT_TILE_BYTES = 64 * 1024
+
+# kernels launched by CopyTable.launch in this process (benchmarks report it)
+LAUNCH_COUNT = [0]
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    return _DT_CODE.get(dt, L.DT_RAW)
+
+
+@dataclass
+class SliceRef:
+    """A strided box in some GPU's memory: address of element [0,...,0], element strides, allocation bounds."""
+
+    ptr: int
+    strides: tuple[int, ...]
+    dtype: torch.dtype
+    lo: int = 0  # allocation [lo, hi) the box must stay inside (0, 0 = unchecked)
+    hi: int = 0
+
+    @staticmethod
+    def of(view: torch.Tensor) -> "SliceRef":
+        st = view.untyped_storage()
+        base = st.data_ptr()
+        return SliceRef(view.data_ptr(), tuple(view.stride()), view.dtype, base, base + st.nbytes())
+
+
+class CopyTable:
+    def __init__(self, device: torch.device | int | str, tile_bytes: int = DEFAULT_TILE_BYTES):
+        self.device = torch.device(device) if not isinstance(device, torch.device) else device
+        self.tile_bytes = int(tile_bytes)
+        self._lib = L.cuda_lib()
+        self._op_size = self._lib.etha_sizeof_op()
+        self._packed: list[tuple[int, int, bytes]] = []  # (class, tiles, op bytes)
+        self.payload_bytes = 0  # bytes delivered (destination side, all replicas)
+        self.read_bytes = 0
+        self._final = False
+        self._keepalive: list = []
+        self.n_ops = [0, 0]
+        self.n_tiles = [0, 0]
+
+    # ---- building ---------------------------------------------------------------------------
+    def add(
+        self,
+        shape: Sequence[int],
+        srcs: Sequence[SliceRef],
+        dsts: Sequence[SliceRef],
+        reduce_sizes: Sequence[int] = (),
+        reduce_ops: Sequence[str] = (),
+        multimem: bool = False,
+    ) -> None:
+        """One op: `srcs` (1, or a Partial family in family order) -> every slice of `dsts`."""
+        if self._final:
+            raise RuntimeError("table already finalized")
+        if len(shape) > 8:
+            raise ValueError("at most 8 dims")
+        if len(srcs) > L.MAX_SRC:
+            raise ValueError(f"at most {L.MAX_SRC} Partial contributors per cell are supported on the device")
+        if len(reduce_sizes) > 2:
+            raise ValueError("at most two Partial mesh dims are supported on the device")
+        src0 = srcs[0]
+        for s in srcs[1:]:
+            if s.strides != src0.strides or s.dtype != src0.dtype:
+                raise ValueError("Partial contributors must share strides and dtype")
+        # group destinations by (strides, dtype): one op per group of at most MAX_DST
+        groups: dict[tuple, list[SliceRef]] = {}
+        for d in dsts:
+            groups.setdefault((d.strides, d.dtype), []).append(d)
+        numel = int(np.prod(shape)) if len(shape) else 1
+        for (dstrides, ddtype), members in groups.items():
+            for k in range(0, len(members), L.MAX_DST):
+                part = members[k : k + L.MAX_DST]
+                spec = L.OpSpec()
+                spec.ndim = len(shape)
+                for i, n in enumerate(shape):
+                    spec.shape[i] = int(n)
+                    spec.src_stride[i] = int(src0.strides[i])
+                    spec.dst_stride[i] = int(dstrides[i])
+                spec.src_itemsize, spec.dst_itemsize = src0.dtype.itemsize, ddtype.itemsize
+                spec.src_dtype, spec.dst_dtype = dtype_code(src0.dtype), dtype_code(ddtype)
+                if spec.src_dtype == L.DT_RAW and spec.dst_dtype == L.DT_RAW and src0.dtype != ddtype:
+                    raise ValueError(f"no conversion from {src0.dtype} to {ddtype}")
+                spec.nsrc, spec.ndst = len(srcs), len(part)
+                for i, s in enumerate(srcs):
+                    spec.src[i], spec.src_lo[i], spec.src_hi[i] = s.ptr, s.lo, s.hi
+                for i, d in enumerate(part):
+                    spec.dst[i], spec.dst_lo[i], spec.dst_hi[i] = d.ptr, d.lo, d.hi
+                sizes = list(reduce_sizes) or [len(srcs)]
+                ops = list(reduce_ops) or ["sum"]
+                spec.red_size[0], spec.red_size[1] = sizes[0], (sizes[1] if len(sizes) > 1 else 1)
+                spec.red_op[0] = L.RED_CODES[ops[0]]
+                spec.red_op[1] = L.RED_CODES[ops[1]] if len(ops) > 1 else 0
+                spec.flags = L.FLAG_MULTIMEM if multimem else 0
+                spec.tile_bytes = self.tile_bytes
+                buf = C.create_string_buffer(self._op_size)
+                err = C.create_string_buffer(512)
+                rc = self._lib.etha_pack_op(C.byref(spec), buf, err, 512)
+                if rc != 0:
+                    raise ValueError(f"cannot pack op ({rc}): {err.value.decode(errors='replace')}")
+                tiles = self._lib.etha_op_tiles(buf)
+                if tiles:
+                    cls = self._lib.etha_op_class(buf)
+                    self._packed.append((cls, tiles, buf.raw))
+                mult = 1 if not multimem else 1
+                self.payload_bytes += numel * ddtype.itemsize * len(part) * mult
+        self.read_bytes += numel * src0.dtype.itemsize * len(srcs)
+
+    def add_copy(self, src: torch.Tensor, dst: torch.Tensor) -> None:
+        """Local convenience: copy (and convert) `src` view into `dst` view of the same shape."""
+        if tuple(src.shape) != tuple(dst.shape):
+            raise ValueError(f"shape mismatch {tuple(src.shape)} vs {tuple(dst.shape)}")
+        self._keepalive += [src, dst]
+        self.add(tuple(src.shape), [SliceRef.of(src)], [SliceRef.of(dst)])
+
+    def add_reduce(self, srcs: Sequence[torch.Tensor], dst: torch.Tensor, sizes: Sequence[int], ops: Sequence[str]) -> None:
+        self._keepalive += list(srcs) + [dst]
+        self.add(tuple(dst.shape), [SliceRef.of(s) for s in srcs], [SliceRef.of(dst)], sizes, ops)
+
+    # ---- upload -----------------------------------------------------------------------------
+    def finalize(self, sm_count: int | None = None) -> "CopyTable":
+        if self._final:
+            return self
+        if sm_count is None:
+            sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.sm_count = sm_count
+        self._ops_dev: list[torch.Tensor | None] = [None, None]
+        self._tiles_dev: list[torch.Tensor | None] = [None, None]
+        for cls in (0, 1):
+            members = [(t, raw) for c, t, raw in self._packed if c == cls]
+            self.n_ops[cls] = len(members)
+            if not members:
+                continue
+            starts = np.zeros(len(members) + 1, dtype=np.uint64)
+            np.cumsum([t for t, _ in members], out=starts[1:])
+            if starts[-1] >= 2**32:
+                raise ValueError("too many tiles in one table")
+            self.n_tiles[cls] = int(starts[-1])
+            blob = np.frombuffer(b"".join(raw for _, raw in members), dtype=np.uint8)
+            self._ops_dev[cls] = torch.from_numpy(blob.copy()).to(self.device)
+            self._tiles_dev[cls] = torch.from_numpy(starts.astype(np.uint32).view(np.int32).copy()).to(self.device)
+        self._sync = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._packed = []
+        self._final = True
+        return self
+
+    @property
+    def empty(self) -> bool:
+        return self.n_tiles[0] + self.n_tiles[1] == 0
+
+    # ---- launch -----------------------------------------------------------------------------
+    def launch(
+        self,
+        stream: torch.cuda.Stream | None = None,
+        signals: torch.Tensor | None = None,
+        epoch: int = 0,
+        ctas_per_sm: int = 2,
+        bulk: bool = False,
+    ) -> None:
+        """Enqueue the table on `stream`. `signals`: int64 device tensor of flag addresses to publish `epoch` to."""
+        if not self._final:
+            self.finalize()
+        s = (stream or torch.cuda.current_stream(self.device)).cuda_stream
+        n_sig = 0 if signals is None else signals.numel()
+        sig_ptr = 0 if signals is None else signals.data_ptr()
+        classes = [c for c in (0, 1) if self.n_tiles[c]]
+        if not classes:
+            if n_sig:
+                L.check(self._lib.etha_set_flags(sig_ptr, n_sig, epoch & 0xFFFFFFFF, s), "set_flags")
+                LAUNCH_COUNT[0] += 1
+            return
+        for c in classes:
+            last = c == classes[-1]
+            grid = min(self.n_tiles[c], self.sm_count * ctas_per_sm)
+            if bulk and c == 0 and hasattr(self._lib, "etha_m2n_bulk_launch"):
+                rc = self._lib.etha_m2n_bulk_launch(
+                    self._ops_dev[c].data_ptr(), self._tiles_dev[c].data_ptr(), self.n_ops[c],
+                    min(self.n_tiles[c], self.sm_count), self._sync.data_ptr(), sig_ptr, n_sig if last else 0,
+                    epoch & 0xFFFFFFFF, 1 if (last and n_sig) else 0, s,
+                )
+            else:
+                rc = self._lib.etha_m2n_launch(
+                    self._ops_dev[c].data_ptr(), self._tiles_dev[c].data_ptr(), self.n_ops[c], c, grid, 0,
+                    self._sync.data_ptr(), sig_ptr, n_sig if last else 0, epoch & 0xFFFFFFFF,
+                    1 if (last and n_sig) else 0, s,
+                )
+            L.check(rc, "m2n launch")
+            LAUNCH_COUNT[0] += 1
+
+    def error_word(self) -> int:
+        """Device-side error word of the last launches (synchronizes)."""
+        return int(self._sync[1].item())

@@ -1,0 +1,129 @@
+"""Peer pointers: describe local device tensors so that other processes can address them, and map theirs.
+
+An agent (or a rank of a torchrun job) exports the allocation behind each registered tensor once as a
+64-byte CUDA IPC handle, ships `(handle, offset, shape, strides, dtype)` to its peers over the control
+plane and maps the handles it receives; the copy kernels then use the mapped addresses directly over
+NVLink.  Within one process (a rank that holds both roles, or several logical ranks sharing a GPU) the
+owner's own addresses are used and nothing is mapped.
+
+The reference shares tensors only worker -> agent, by pickling whole tensors through torch's CUDA-IPC
+reducer and rebuilding them on `LOCAL_RANK` (src/etha/tensor_bus/client.py:314, src/etha/tensor_bus/
+agent.py:608, src/etha/tensor_bus/utils.py:14-69); agents never see each other's memory there.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+
+import torch
+
+from ..ops import lib as L
+from ..ops.table import SliceRef
+
+_DTYPE_NAMES = {str(d).replace("torch.", ""): d for d in [
+    torch.float32, torch.float64, torch.float16, torch.bfloat16, torch.int8, torch.uint8, torch.int16,
+    torch.int32, torch.int64, torch.bool, torch.float8_e4m3fn, torch.float8_e5m2,
+]}
+
+
+@dataclass(frozen=True)
+class RegionDesc:
+    """One exported device allocation."""
+
+    pid: int
+    device_index: int
+    base: int  # address in the owner's address space
+    size: int
+    handle: bytes  # cudaIpcMemHandle_t
+
+    @property
+    def key(self) -> tuple:
+        return (self.pid, self.device_index, self.base)
+
+
+@dataclass(frozen=True)
+class TensorDesc:
+    """A (possibly strided) tensor inside an exported allocation."""
+
+    region: RegionDesc
+    offset: int  # bytes from region.base to element [0, ..., 0]
+    shape: tuple[int, ...]
+    strides: tuple[int, ...]  # elements
+    dtype: str
+
+    @property
+    def torch_dtype(self) -> torch.dtype:
+        return _DTYPE_NAMES[self.dtype]
+
+
+class PeerMemory:
+    """Per-process registry of exported and mapped allocations."""
+
+    def __init__(self, device: torch.device | int | None = None):
+        if device is None:
+            device = torch.cuda.current_device()
+        self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+        self.pid = os.getpid()
+        self._lib = L.cuda_lib()
+        self._exported: dict[int, RegionDesc] = {}  # base -> desc
+        self._mapped: dict[tuple, int] = {}  # region key -> local base
+        self._keepalive: list[torch.Tensor] = []
+
+    # ---- owner side -----------------------------------------------------------------------
+    def describe(self, t: torch.Tensor, keepalive: bool = True) -> TensorDesc:
+        if not t.is_cuda:
+            raise ValueError("only CUDA tensors can be exported")
+        with torch.cuda.device(t.device):
+            handle = C.create_string_buffer(64)
+            base, size = C.c_uint64(), C.c_uint64()
+            storage_ptr = t.untyped_storage().data_ptr()
+            L.check(self._lib.etha_ipc_export(storage_ptr, handle, C.byref(base), C.byref(size)), "ipc_export")
+        region = self._exported.get(base.value)
+        if region is None or region.size != size.value:
+            region = RegionDesc(self.pid, t.device.index, base.value, size.value, handle.raw)
+            self._exported[base.value] = region
+        if keepalive:
+            self._keepalive.append(t)
+        return TensorDesc(region, t.data_ptr() - base.value, tuple(t.shape), tuple(t.stride()),
+                          str(t.dtype).replace("torch.", ""))
+
+    def describe_local_only(self, t: torch.Tensor) -> TensorDesc:
+        """Descriptor usable only inside this process (no IPC handle is created)."""
+        st = t.untyped_storage()
+        region = RegionDesc(self.pid, t.device.index if t.is_cuda else -1, st.data_ptr(), st.nbytes(), b"")
+        self._keepalive.append(t)
+        return TensorDesc(region, t.data_ptr() - st.data_ptr(), tuple(t.shape), tuple(t.stride()),
+                          str(t.dtype).replace("torch.", ""))
+
+    # ---- peer side ------------------------------------------------------------------------
+    def map_region(self, region: RegionDesc) -> int:
+        """Address of `region.base` in this process (maps the allocation on first use)."""
+        if region.pid == self.pid:
+            return region.base
+        local = self._mapped.get(region.key)
+        if local is None:
+            if not region.handle:
+                raise ValueError("region of another process was exported without an IPC handle")
+            with torch.cuda.device(self.device):
+                out = C.c_uint64()
+                L.check(self._lib.etha_ipc_open(region.handle, C.byref(out)), "ipc_open")
+            local = out.value
+            self._mapped[region.key] = local
+        return local
+
+    def slice_ref(self, desc: TensorDesc, index: tuple[slice, ...] = ()) -> SliceRef:
+        """`SliceRef` of `tensor[index]` (unit-step slices) for the tensor described by `desc`."""
+        base = self.map_region(desc.region)
+        dt = desc.torch_dtype
+        off = desc.offset
+        for sl, stride in zip(index, desc.strides):
+            off += (sl.start or 0) * stride * dt.itemsize
+        return SliceRef(base + off, desc.strides, dt, base, base + desc.region.size)
+
+    def close(self) -> None:
+        for local in self._mapped.values():
+            self._lib.etha_ipc_close(local)
+        self._mapped.clear()
+        self._keepalive.clear()
