@@ -172,7 +172,9 @@ class _Engine:
                 }
                 for k, (c, w) in enumerate(zip(b.chunks, wire_views)):
                     vals = [c.src_view() if q == self.rank else contrib_views[q][k] for q in fam.ranks]
-                    w.copy_(reduce_family_values(vals, fam, c.transfer_dtype))
+                    # collapse in fp32, round once to the source dtype (what Partial -> Replicate yields),
+                    # then convert to the wire dtype
+                    w.copy_(reduce_family_values(vals, fam, src_dtype))
         # local consumers (a rank on both meshes may be one of the consumers of its own cells)
         if single_inplace:
             c = b.head

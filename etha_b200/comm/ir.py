@@ -134,7 +134,9 @@ def reduce_family_values(values: Sequence[torch.Tensor], family: PartialFamily, 
     """Reference arithmetic of the Partial collapse, shared by the CPU executor and the kernel tests.
 
     Floating inputs are accumulated in fp32 (fp64 stays fp64) in ascending family order, one level
-    per Partial mesh dim, and rounded once to `out_dtype`.  Integer inputs accumulate in int64.
+    per Partial mesh dim, and rounded once to `out_dtype` — callers pass the source dtype, the dtype a
+    Partial -> Replicate redistribution yields, and convert to the wire / target dtype afterwards.
+    Integer inputs accumulate in int64.
     """
     src_dtype = values[0].dtype
     if src_dtype == torch.float64:

@@ -246,8 +246,17 @@ __device__ __forceinline__ void tile_cvt1(const M2NOp& op, uint32_t base, uint32
   }
 }
 
+template <int DT>
+__device__ __forceinline__ float round_through(float x) {
+  if constexpr (DT == M2N_BF16) return __bfloat162float(__float2bfloat16_rn(x));
+  if constexpr (DT == M2N_F16) return __half2float(__float2half_rn(x));
+  return x;
+}
+
 // Partial collapse: level 0 groups of red_size[0] consecutive sources, then level 1 over the group results;
-// fp32 accumulation in ascending source order, "avg" divides by the group size, one rounding at the store.
+// fp32 accumulation in ascending source order, "avg" divides by the group size.  The collapsed value is
+// rounded once to the SOURCE dtype (the dtype a Partial -> Replicate redistribution yields) and then converted
+// to the destination dtype, so a two-way sum is bit-identical to an all-reduce in the source dtype.
 template <int SDT, int DDT, int N>
 __device__ __forceinline__ void tile_reduce(const M2NOp& op, uint32_t base, uint32_t limit, int unroll) {
   const int s0 = op.red_size[0], s1 = op.red_size[1];
@@ -281,6 +290,10 @@ __device__ __forceinline__ void tile_reduce(const M2NOp& op, uint32_t base, uint
     if (op1 == M2N_AVG && s1 > 1) {
 #pragma unroll
       for (int k = 0; k < N; ++k) acc[k] = __fdiv_rn(acc[k], (float)s1);
+    }
+    if constexpr (SDT != DDT) {
+#pragma unroll
+      for (int k = 0; k < N; ++k) acc[k] = round_through<SDT>(acc[k]);
     }
     for (int j = 0; j < op.ndst; ++j) {
       char* d = reinterpret_cast<char*>(op.dst[j]) + dof;

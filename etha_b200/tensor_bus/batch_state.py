@@ -1,0 +1,25 @@
+"""In-memory state of one registered batch on an agent (reference: src/etha/tensor_bus/batch_state.py:17-43)."""
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+
+
+@dataclass(kw_only=True)
+class BatchState:
+    batch_id: str
+    pair_names: list[str]
+    local_leader: int | None = None
+    local_ranks: list[int] = field(default_factory=list)
+    remote_ranks: list[int] = field(default_factory=list)
+    pair_tensors: dict[str, list[Any]] = field(default_factory=dict)  # local tensors (CPU) or descriptors (CUDA)
+    pair_target_dtypes: dict[str, list[torch.dtype]] = field(default_factory=dict)
+    bucket_size: int | None = None
+    # executors, one per direction; which type depends on where the tensors live
+    send_exec: Any = None
+    recv_exec: Any = None
+    send_buckets: list | None = None
+    recv_buckets: list | None = None
+    epoch: int = 0
+    keepalive: list = field(default_factory=list)

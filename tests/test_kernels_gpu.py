@@ -114,7 +114,7 @@ def test_partial_collapse_matches_reference_arithmetic(sizes, opnames, sdt, ddt)
     t.add_reduce(srcs, dst, sizes, opnames)
     _run(t)
     fam = PartialFamily(ranks=tuple(range(n)), sizes=tuple(sizes), ops=tuple(opnames))
-    want = reduce_family_values([s.cpu() for s in srcs], fam, ddt)
+    want = reduce_family_values([s.cpu() for s in srcs], fam, sdt).to(ddt)
     assert torch.equal(dst.cpu(), want)
     for s, i in zip(srcs, range(n)):
         assert torch.equal(s, _rand((256, 520), sdt, 100 + i)), "sources must stay untouched"

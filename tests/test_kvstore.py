@@ -1,0 +1,134 @@
+"""KV store behaviours on both backends (TCPStore in-process; etcd through an in-process JSON gateway).
+Mirrors the behaviour list of the reference's tests/test_kvstore.py."""
+
+import threading
+import time
+
+import pytest
+
+from etha_b200.kvstore import EtcdStore, TorchTCPStore, create_store
+from etha_b200.kvstore.fake_etcd import FakeEtcdGateway
+
+from conftest import free_port
+
+
+@pytest.fixture(params=["tcp", "etcd"])
+def store(request):
+    if request.param == "tcp":
+        s = TorchTCPStore("127.0.0.1", free_port(), world_size=1, is_master=True, timeout=10.0,
+                          wait_for_workers=False, namespace="ns", component="tensorbus")
+        yield s
+        s.close()
+    else:
+        gw = FakeEtcdGateway().start()
+        s = EtcdStore(gw.host, gw.port, timeout=5.0, namespace="ns")
+        yield s
+        s.close()
+        gw.stop()
+
+
+def test_set_get_exists_delete(store):
+    assert store.get("a") is None and not store.exists("a")
+    store.set("a", "1")
+    assert store.get("a") == b"1" and store.exists("a")
+    store.set("a", "2")
+    assert store.get("a") == b"2"
+    assert store.delete("a") is True
+    assert not store.try_get("a")
+    assert store.delete("never-there") is False
+
+
+def test_bytes_roundtrip(store):
+    blob = bytes(range(256)) * 9
+    store.set_bytes("blob", blob)
+    assert store.get_bytes("blob") == blob
+    assert store.get_bytes("missing") is None
+
+
+def test_component_and_namespace_isolation(store):
+    store.set("k", "local")
+    store.set("k", "global", component="global")
+    assert store.get("k") == b"local" and store.get("k", component="global") == b"global"
+    assert store._prefixed("k") == "ns/tensorbus/k" and store._strip_prefix("ns/tensorbus/pair:x/rank:1/y") == "pair:x/rank:1/y"
+    if isinstance(store, EtcdStore):
+        other = EtcdStore(store.host, store.port, namespace="other")
+        assert other.get("k") is None
+        other.close(cleanup=False)
+
+
+def test_wait_for_key_existing_async_timeout(store):
+    store.set("ready", "yes")
+    assert store.wait_for_key("ready", timeout=1.0) == b"yes"
+    threading.Timer(0.15, lambda: store.set("later", "v")).start()
+    t0 = time.monotonic()
+    assert store.wait_for_key("later", timeout=5.0) == b"v"
+    assert 0.1 < time.monotonic() - t0 < 3.0
+    with pytest.raises(TimeoutError):
+        store.wait_for_key("never", timeout=0.1)
+
+
+def test_wait_for_value(store):
+    store.set("state", "0")
+    threading.Timer(0.1, lambda: store.set("state", "1")).start()
+    assert store.wait_for_value("state", "1", timeout=5.0) == b"1"
+    with pytest.raises(TimeoutError):
+        store.wait_for_value("state", "7", timeout=0.1)
+
+
+def test_wait_for_keys_pattern_value_and_async(store):
+    cands = [f"pair:p/rank:{r}/trainer" for r in range(8)]
+    for r in (0, 1):
+        store.set(cands[r], "1")
+    store.set("pair:p/rank:5/trainer", "0")  # wrong value: must not count
+    store.set("pair:q/rank:0/trainer", "1")  # other pair: must not match
+    got = store.wait_for_keys("pair:p/rank:*/trainer", 2, timeout=1.0, candidate_keys=cands)
+    assert got == [cands[0], cands[1]]
+
+    def writer():
+        time.sleep(0.1)
+        store.set(cands[2], "1")
+        store.set(cands[3], "1")
+
+    threading.Thread(target=writer).start()
+    got = store.wait_for_keys("pair:p/rank:*/trainer", 4, timeout=5.0, candidate_keys=cands)
+    assert got == cands[:4]
+    with pytest.raises(TimeoutError, match="got 4"):
+        store.wait_for_keys("pair:p/rank:*/trainer", 6, timeout=0.1, candidate_keys=cands)
+    assert store.poll_keys("pair:p/rank:*/trainer", "0", cands) == ["pair:p/rank:5/trainer"]
+
+
+def test_tcp_needs_candidate_keys_etcd_does_not(store):
+    store.set("x/1", "1")
+    if isinstance(store, TorchTCPStore):
+        with pytest.raises(ValueError, match="candidate_keys"):
+            store.wait_for_keys("x/*", 1, timeout=0.1)
+    else:
+        assert store.wait_for_keys("x/*", 1, timeout=1.0) == ["x/1"]
+
+
+def test_etcd_cleanup_removes_namespace():
+    gw = FakeEtcdGateway().start()
+    a = EtcdStore(gw.host, gw.port, namespace="n1")
+    b = EtcdStore(gw.host, gw.port, namespace="n2")
+    a.set("k", "1"), b.set("k", "1")
+    a.close(cleanup=True)
+    assert b.get("k") == b"1"
+    c = EtcdStore(gw.host, gw.port, namespace="n1")
+    assert c.get("k") is None
+    gw.stop()
+
+
+def test_etcd_unreachable_fails_fast():
+    with pytest.raises(ConnectionError):
+        EtcdStore("127.0.0.1", free_port(), timeout=0.5)
+
+
+def test_create_store_factory(monkeypatch):
+    monkeypatch.setenv("RANK", "0")
+    monkeypatch.setenv("WORLD_SIZE", "1")
+    s = create_store("127.0.0.1", free_port(), backend="tcp", timeout=10.0, namespace="abc")
+    assert isinstance(s, TorchTCPStore) and s.is_master and s.namespace == "abc"
+    gw = FakeEtcdGateway().start()
+    e = create_store(gw.host, gw.port, backend="etcd", namespace="abc")
+    assert isinstance(e, EtcdStore)
+    gw.stop()
