@@ -1,0 +1,203 @@
+"""Runs the reference's own executor (`etha.comm`: get_m2m_map -> m2m_to_chunks -> chunk_to_bucket_ops ->
+bucket_comm over NCCL) on the benchmark's model and layouts, from the unmodified copy under `baseline/_ref`.
+
+Nothing of this repository's planner, executors or kernels is on that path; only the weight shapes, the seeded
+random initialisation and the timing protocol are shared.  The reference imports `lmdb`, `posix_ipc`, `etcd3`
+and `upath` at package import although `etha.comm` never uses them; those four are absent on this image, so
+empty stand-in modules are registered before the import (the reference's files are not touched).
+Timing follows the reference's own benchmark (bench/transfer_benchmark.py:201-210): barrier, CUDA events around K
+back-to-back `bucket_comm` calls — except that every rank times itself and the maximum is reported.
+With one GPU the reference cannot plan (its tracing planner sends to itself and never posts the receive), so
+the single-GPU case runs its `Transport.LOCAL` chunks built by hand, the path its own test exercises
+(tests/test_self_copy_bucket.py:34-63).
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+import types
+
+
+def _install_stubs() -> None:
+    def mod(name, **attrs):
+        if name in sys.modules:
+            return
+        try:
+            __import__(name)
+            return
+        except Exception:
+            pass
+        m = types.ModuleType(name)
+        for k, v in attrs.items():
+            setattr(m, k, v)
+        sys.modules[name] = m
+
+    class _Err(Exception):
+        pass
+
+    mod("lmdb", Environment=object, open=lambda *a, **k: (_ for _ in ()).throw(RuntimeError("lmdb stub")))
+    mod("posix_ipc", Semaphore=object, BusyError=_Err, ExistentialError=_Err, O_CREAT=0o100, O_EXCL=0o200,
+        unlink_semaphore=lambda name: None)
+    mod("etcd3", client=lambda *a, **k: (_ for _ in ()).throw(RuntimeError("etcd3 stub")))
+    import pathlib
+
+    mod("upath", UPath=pathlib.Path)
+
+
+def run(args, ref_dir: str) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if root not in sys.path:
+        sys.path.insert(0, root)
+    _install_stubs()
+    sys.path.insert(0, ref_dir)
+    from bench import init_dist, max_over_ranks, meshes_for, model_of  # shared harness pieces only
+
+    rank, world, group = init_dist(args.gpus)
+    if world == 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("cuda:nccl,cpu:gloo", rank=0, world_size=1)
+    try:
+        from etha.comm import bucket_comm, chunk_to_bucket_ops, get_m2m_map, m2m_to_chunks
+        from etha.comm.ir import Chunk, Transport
+    except Exception as e:  # pragma: no cover - depends on the box
+        if rank == 0:
+            return {"impl": "reference", "unavailable": f"import of the reference failed: {type(e).__name__}: {e}"[:300]}
+        return {}
+    from torch.distributed.device_mesh import DeviceMesh
+
+    from etha_b200.models import fsdp_layout, vllm_tp_layout
+    from etha_b200.models.sync import full_tensor_for, local_shape_and_offset
+    from etha_b200.utils.clocks import ClockSampler
+    from torch.distributed.tensor.placement_types import Replicate
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    model = model_of(args.model)
+    smesh_t, tmesh_t, par = meshes_for(world)
+    s_rule, t_rule = fsdp_layout(), vllm_tp_layout()
+    is_src, is_dst = rank in smesh_t.tolist(), rank in tmesh_t.tolist()
+    dtype = torch.bfloat16
+    seed = 2
+
+    def shard(spec, k, mesh_t, plc):
+        full = full_tensor_for(spec, k, seed, torch.float32, dev)
+        shape, off = local_shape_and_offset(spec.shape, mesh_t, plc, rank)
+        out = full[tuple(slice(o, o + n) for o, n in zip(off, shape))].to(dtype).contiguous()
+        del full
+        return out
+
+    chunks = []
+    targets = []
+    payload = 0
+    if world > 1:
+        smesh = DeviceMesh("cpu", smesh_t)
+        tmesh = DeviceMesh("cpu", tmesh_t)
+        maps = {}
+        for k, spec in enumerate(model.tensors):
+            sp, tp = tuple(s_rule(spec)), tuple(t_rule(spec))
+            if (sp, tp) not in maps:
+                maps[(sp, tp)] = get_m2m_map(smesh, sp, tmesh, tp, group=dist.group.WORLD, device="cpu")
+            src = shard(spec, k, smesh_t, sp) if is_src else None
+            tgt = None
+            if is_dst:
+                shape, _ = local_shape_and_offset(spec.shape, tmesh_t, tp, rank)
+                tgt = torch.zeros(shape, dtype=dtype, device=dev)
+                targets.append((k, spec, tp, tgt))
+            chunks += m2m_to_chunks(maps[(sp, tp)], rank=rank, source_tensor=src, target_tensor=tgt)
+            copies = 1
+            for size, p in zip(tmesh_t.shape, tp):
+                if isinstance(p, Replicate):
+                    copies *= size
+            n = dtype.itemsize
+            for s in spec.shape:
+                n *= s
+            payload += n * copies
+    else:
+        # one GPU: hand-built LOCAL chunks; source and target of a parameter are the two halves of one tensor,
+        # because a LOCAL chunk reads and writes the same `tensor`
+        for k, spec in enumerate(model.tensors):
+            both = torch.zeros((2, *spec.shape), dtype=dtype, device=dev)
+            both[0].copy_(shard(spec, k, smesh_t, tuple(s_rule(spec))))
+            nd = len(spec.shape)
+            chunks.append(Chunk(
+                chunk_shape=(1, *spec.shape), transport=Transport.LOCAL, is_source=True, is_target=True, src_rank=0,
+                src_idx=(0,) * (nd + 1), dst_ranks=(0,), dst_idx=(1,) + (0,) * nd,
+                src_slice=(slice(0, 1),) + (slice(None),) * nd, dst_slice=(slice(1, 2),) + (slice(None),) * nd,
+                tensor=both,
+            ))
+            targets.append((k, spec, tuple(t_rule(spec)), both[1]))
+            n = dtype.itemsize
+            for s in spec.shape:
+                n *= s
+            payload += n
+
+    modes = {"chunk": 1}
+    if args.bucket_mb > 0:
+        modes[f"bucket{args.bucket_mb}MiB"] = args.bucket_mb << 20
+    results = {}
+    clocks = {}
+    bad = 0
+    for name, bucket_size in modes.items():
+        buckets = chunk_to_bucket_ops(chunks=chunks, bucket_size=bucket_size)
+        for _ in range(args.warmup):
+            bucket_comm(buckets=buckets)
+        torch.cuda.synchronize()
+        if not args.no_verify and not results:
+            for k, spec, tp, tgt in targets:
+                full = full_tensor_for(spec, k, seed, torch.float32, dev).to(dtype)
+                shape, off = local_shape_and_offset(spec.shape, tmesh_t, tp, rank)
+                if not torch.equal(tgt, full[tuple(slice(o, o + n) for o, n in zip(off, shape))]):
+                    bad += 1
+                del full
+        sampler = ClockSampler(dev.index).start()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            bucket_comm(buckets=buckets)
+        e1.record()
+        torch.cuda.synchronize()
+        clocks[name] = sampler.stop()
+        results[name] = max_over_ranks(e0.elapsed_time(e1), world) / args.steps
+        dist.barrier()
+    bad = int(max_over_ranks(float(bad), world))
+    best = min(results, key=results.get)
+    ms = results[best]
+    out = {
+        "metric": "weight_sync_GBps",
+        "value": round(payload / (ms * 1e-3) / 1e9, 2),
+        "unit": "GB/s (1e9 bytes held by consumers / device time, max over ranks)",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(ms, 4),
+        "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic: random-init weights (randn*0.02, seeded per tensor), no checkpoint",
+        "impl": "reference",
+        "config": {
+            "model": args.model,
+            "parallelism": par,
+            "tensors": len(model.tensors),
+            "payload_bytes": payload,
+            "executor": "reference etha.comm.bucket_comm over NCCL" if world > 1 else "reference LOCAL chunks (hand-built), bucket_comm",
+            "mode_reported": best,
+            "ms_per_step_by_mode": {k: round(v, 4) for k, v in results.items()},
+            "l2_policy": "inputs larger than L2",
+            "verified_bit_exact": bad == 0 if not args.no_verify else None,
+        },
+        "e2e": {"value": round(payload / (ms * 1e-3) / 1e9, 2), "unit": "GB/s",
+                "what": "bucket_comm is the reference's public call and ends with a device synchronize; no separate end-to-end path",
+                "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "clocks": clocks[best],
+    }
+    dist.destroy_process_group()
+    return out if rank == 0 else {}
