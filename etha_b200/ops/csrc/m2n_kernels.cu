@@ -517,3 +517,137 @@ int etha_wait_flags(const uint32_t* flags, const uint32_t* which, uint32_t n, ui
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free entry point (declared in no_alloc.h).  Same kernels as above; the op table, the tile
+// prefix sums and the counters live in a resident array instead of caller-allocated device buffers.
+// ---------------------------------------------------------------------------------------------------
+#include <mutex>
+
+#include "no_alloc.h"
+
+namespace {
+
+static_assert(sizeof(M2NOp) <= 320, "scratch layout assumes ops of at most 320 bytes");
+
+// layout: [0,256) counters of the fast launch, [256,512) counters of the general launch,
+//         [512,1280) tile_start of the fast class, [1280,2048) tile_start of the general class,
+//         [2048, ...) ops: fast class first, general class after it
+static __device__ __align__(256) unsigned char g_noalloc_scratch[ETHA_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+unsigned char* g_noalloc_ptr[kMaxDevices] = {nullptr};
+int g_noalloc_sms[kMaxDevices] = {0};
+
+// Host code must not use `g_noalloc_scratch` as an address: there it is only a stand-in for the symbol.
+// The device address is queried once per device, with that device current.
+int noalloc_setup(int dev, unsigned char** out, int* sms) {
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (dev < 0 || dev >= kMaxDevices) {
+    snprintf(etha_err_buf(), ETHA_ERR_LEN, "device index %d out of range", dev);
+    return -101;
+  }
+  if (!g_noalloc_ptr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || !p) return fail(e, "cudaGetSymbolAddress(scratch)");
+    int n = 0;
+    e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return fail(e, "cudaDeviceGetAttribute(sm count)");
+    g_noalloc_sms[dev] = n;
+    g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  *sms = g_noalloc_sms[dev];
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int etha_pack_op(const M2NOpSpec* spec, M2NOp* out, char* err, int err_len);
+extern "C" uint32_t etha_op_tiles(const M2NOp* op);
+extern "C" int etha_op_class(const M2NOp* op);
+
+extern "C" int etha_m2n_run_noalloc(const M2NOpSpec* specs, uint32_t n_specs, int ctas_per_sm, void* stream) {
+  if (!specs && n_specs) {
+    snprintf(etha_err_buf(), ETHA_ERR_LEN, "null spec array");
+    return -101;
+  }
+  if (n_specs > ETHA_NOALLOC_MAX_OPS) {
+    snprintf(etha_err_buf(), ETHA_ERR_LEN, "%u ops requested, the allocation-free entry point takes at most %d per call",
+             n_specs, ETHA_NOALLOC_MAX_OPS);
+    return -100;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(e, "cudaGetDevice");
+  unsigned char* scratch = nullptr;
+  int sms = 0;
+  int rc = noalloc_setup(dev, &scratch, &sms);
+  if (rc != 0) return rc;
+
+  // host staging lives in thread-local storage: no heap allocation per call
+  static thread_local M2NOp packed[2][ETHA_NOALLOC_MAX_OPS];
+  static thread_local uint32_t tile_start[2][ETHA_NOALLOC_MAX_OPS + 1];
+  uint32_t count[2] = {0, 0};
+  tile_start[0][0] = tile_start[1][0] = 0;
+  for (uint32_t i = 0; i < n_specs; ++i) {
+    M2NOp op;
+    rc = etha_pack_op(&specs[i], &op, etha_err_buf(), ETHA_ERR_LEN);
+    if (rc != 0) return rc;
+    const uint32_t tiles = etha_op_tiles(&op);
+    if (!tiles) continue;
+    const int c = etha_op_class(&op);
+    const uint64_t next = (uint64_t)tile_start[c][count[c]] + tiles;
+    if (next >= (1ull << 32)) {
+      snprintf(etha_err_buf(), ETHA_ERR_LEN, "too many tiles in one call");
+      return -101;
+    }
+    packed[c][count[c]] = op;
+    tile_start[c][++count[c]] = (uint32_t)next;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  // counters must start at zero whatever the previous call left there
+  e = cudaMemsetAsync(scratch, 0, 512, s);
+  if (e != cudaSuccess) return fail(e, "cudaMemsetAsync(scratch counters)");
+  if (ctas_per_sm <= 0) ctas_per_sm = 2;
+  M2NOp* ops_dev = reinterpret_cast<M2NOp*>(scratch + 2048);
+  for (int c = 0; c < 2; ++c) {
+    if (!count[c]) continue;
+    uint32_t* tiles_dev = reinterpret_cast<uint32_t*>(scratch + 512 + 768 * c);
+    M2NOp* class_ops = ops_dev + (c == 0 ? 0 : count[0]);
+    e = cudaMemcpyAsync(tiles_dev, tile_start[c], (count[c] + 1) * sizeof(uint32_t), cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) return fail(e, "cudaMemcpyAsync(tile table)");
+    e = cudaMemcpyAsync(class_ops, packed[c], count[c] * sizeof(M2NOp), cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) return fail(e, "cudaMemcpyAsync(op table)");
+    const uint32_t total = tile_start[c][count[c]];
+    int grid = (int)(total < (uint32_t)(sms * ctas_per_sm) ? total : (uint32_t)(sms * ctas_per_sm));
+    if (grid < 1) grid = 1;
+    uint32_t* sync = reinterpret_cast<uint32_t*>(scratch + 256 * c);
+    if (c == 0)
+      m2n_fast_kernel<<<grid, 512, 0, s>>>(class_ops, tiles_dev, count[c], sync, nullptr, 0, 0, 0);
+    else
+      m2n_general_kernel<<<grid, 256, 0, s>>>(class_ops, tiles_dev, count[c], sync, nullptr, 0, 0, 0);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(e, "allocation-free launch");
+  }
+  return 0;
+}
+
+extern "C" int etha_m2n_noalloc_status(uint32_t* status, void* stream) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(e, "cudaGetDevice");
+  unsigned char* scratch = nullptr;
+  int sms = 0;
+  int rc = noalloc_setup(dev, &scratch, &sms);
+  if (rc != 0) return rc;
+  uint32_t words[2] = {0, 0};
+  e = cudaMemcpyAsync(&words[0], scratch + 4, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(&words[1], scratch + 256 + 4, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(e, "read scratch status");
+  *status = words[0] ? words[0] : words[1];
+  return 0;
+}
