@@ -45,6 +45,25 @@ def _install_stubs() -> None:
     mod("upath", UPath=pathlib.Path)
 
 
+def _arm_watchdog(rank: int, world: int, limit_s: float) -> None:
+    """The reference's unordered NCCL pipeline can stall; after `limit_s` the arm reports that instead of
+    hanging the caller: rank 0 prints the `unavailable` line and every rank leaves with status 0."""
+    import json
+    import threading
+
+    def fire():
+        if rank == 0:
+            print(json.dumps({
+                "impl": "reference",
+                "unavailable": f"the reference's bucket_comm over NCCL did not finish within {limit_s:.0f} s on {world} GPUs",
+            }), flush=True)
+        os._exit(0)
+
+    t = threading.Timer(limit_s, fire)
+    t.daemon = True
+    t.start()
+
+
 def run(args, ref_dir: str) -> dict:
     import torch
     import torch.distributed as dist
@@ -54,13 +73,17 @@ def run(args, ref_dir: str) -> dict:
         sys.path.insert(0, root)
     _install_stubs()
     sys.path.insert(0, ref_dir)
-    from bench import init_dist, max_over_ranks, meshes_for, model_of  # shared harness pieces only
+    from bench import max_over_ranks, meshes_for, model_of  # shared harness pieces only
 
-    rank, world, group = init_dist(args.gpus)
-    if world == 1 and not dist.is_initialized():
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("MASTER_PORT", "29533")
-        dist.init_process_group("cuda:nccl,cpu:gloo", rank=0, world_size=1)
+    # initialise exactly as the reference's agent does (src/etha/tensor_bus/agent.py:103-107): no eager
+    # communicator, so every peer pair gets its own lazily created NCCL communicator and stream
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    _arm_watchdog(rank, world, float(os.environ.get("ETHA_REFERENCE_LIMIT_S", "300")))
+    dist.init_process_group(backend="cuda:nccl,cpu:gloo", rank=rank, world_size=world)
     try:
         from etha.comm import bucket_comm, chunk_to_bucket_ops, get_m2m_map, m2m_to_chunks
         from etha.comm.ir import Chunk, Transport
