@@ -116,6 +116,19 @@ class P2PBatch:
         self._finish_build({e["rank"]: e for e in everyone})
         return self
 
+    def build_from(self, layouts: Sequence[PairLayout], by_rank: dict[int, dict], flags: torch.Tensor) -> "P2PBatch":
+        """Build from descriptors gathered by the caller (the agent exchanges them through its KV store).
+
+        `by_rank[r]` = `{"src": [TensorDesc | None, ...], "dst": [...], "flags": TensorDesc}` with one entry per
+        tensor of the batch, in batch order; `flags` is this rank's own flag array (int32, one slot per rank of
+        `ranks`), the tensor `by_rank[rank]["flags"]` describes.
+        """
+        self._entries = [(layout, None, None) for layout in layouts]
+        self._flags = flags
+        self._status = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self._finish_build(by_rank)
+        return self
+
     def _finish_build(self, by_rank: dict[int, dict]) -> None:
         table = CopyTable(self.device, tile_bytes=self.tile_bytes)
         consumers_i_write: set[int] = set()

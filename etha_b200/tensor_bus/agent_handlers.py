@@ -1,0 +1,349 @@
+"""Command handlers of the agent, written as generators that `yield` whenever they have to wait.
+
+Key layout in the KV store (component `tensorbus` unless noted), same names as the reference where it has
+them (src/etha/tensor_bus/agent.py:224-243, 450-455):
+
+    pair:{p}/rank:{r}/{local_name}             "1"      this agent registered for side `local_name`
+    pair:{p}/{local_name}/expected_world_size  int      ranks on that side
+    pair:{p}/rank:{r}/mesh_shape | placements  pickles  layout of the side `r` belongs to
+    batch:{b}/rank:{r}/meta                    pickle   tensor descriptors + flag arrays of agent `r`   (new)
+    batch:{b}/go:{epoch}/rank:{r}              "1"      agent `r` entered transfer `epoch`               (new)
+    batch:{b}/done:{epoch}/rank:{r}            "1"      producer `r` finished its copies (host completion) (new)
+    batch:{b}/state:transfer_signal            "1"/"0"  component `global`
+"""
+
+from __future__ import annotations
+
+import logging
+import pickle
+import time
+
+import torch
+from torch.distributed.tensor.placement_types import Partial
+
+from ..comm import chunk_to_bucket_ops, m2m_to_chunks
+from ..comm.bucket_exec import bucket_comm
+from ..comm.planner import plan_m2m
+from .batch_state import BatchState
+from .commands import CleanupBatch, InitPair, QueryStatus, RegisterTensors, Transfer
+from .pair_state import PairState
+
+logger = logging.getLogger(__name__)
+
+
+def _wire_dtype(src: torch.dtype, dst: torch.dtype) -> torch.dtype:
+    """Smaller item size wins; on a tie the SOURCE dtype travels and the consumer converts (the reference lets each
+    side pick its own dtype on a tie and reinterprets bytes, src/etha/tensor_bus/agent.py:635-640)."""
+    return src if src.itemsize <= dst.itemsize else dst
+
+
+class AgentHandlers:
+    # ---- InitPair ---------------------------------------------------------------------------------
+    def _init_pair_job(self, msg: InitPair):
+        pair, local_name, remote_name = msg.pair_name, msg.local_name, msg.remote_name
+        store = self.store
+        store.set(f"pair:{pair}/rank:{self.rank}/{local_name}", "1")
+        store.set(f"pair:{pair}/{local_name}/expected_world_size", str(msg.expected_world_size))
+        if msg.mesh_shape_payload is not None and msg.placements_payload is not None:
+            store.set_bytes(f"pair:{pair}/rank:{self.rank}/mesh_shape", bytes(msg.mesh_shape_payload))
+            store.set_bytes(f"pair:{pair}/rank:{self.rank}/placements", bytes(msg.placements_payload))
+
+        def side(name: str, expected: int):
+            cands = [f"pair:{pair}/rank:{r}/{name}" for r in range(self.world_size)]
+            while True:
+                keys = store.poll_keys(f"pair:{pair}/rank:*/{name}", "1", cands)
+                if len(keys) >= expected:
+                    return sorted(self._extract_rank(k) for k in keys)[:expected]
+                yield None
+
+        local_ranks = yield from side(local_name, msg.expected_world_size)
+        while True:
+            raw = store.try_get(f"pair:{pair}/{remote_name}/expected_world_size")
+            if raw:
+                break
+            yield
+        expected_remote = int(raw.decode())
+        remote_ranks = yield from side(remote_name, expected_remote)
+
+        def layout(ranks):
+            infos = []
+            for r in ranks:
+                ms = store.get_bytes(f"pair:{pair}/rank:{r}/mesh_shape")
+                pl = store.get_bytes(f"pair:{pair}/rank:{r}/placements")
+                if ms and pl:
+                    infos.append((tuple(pickle.loads(ms)), tuple(pickle.loads(pl))))
+            if not infos:
+                return None
+            for i, info in enumerate(infos):
+                if info != infos[0]:
+                    raise ValueError(f"pair '{pair}': rank {ranks[i]} declared {info}, rank {ranks[0]} declared {infos[0]}")
+            shape, plc = infos[0]
+            n = 1
+            for s in shape:
+                n *= s
+            if n != len(ranks):
+                raise ValueError(f"pair '{pair}': mesh shape {shape} does not hold {len(ranks)} ranks")
+            # the registered ranks, ascending, fill the mesh row-major (the reference assumes a contiguous range)
+            return torch.tensor(sorted(ranks)).view(shape), plc
+
+        local, remote = layout(local_ranks), layout(remote_ranks)
+        st = PairState(
+            pair_name=pair, local_name=local_name, local_ranks=local_ranks, remote_name=remote_name,
+            remote_ranks=remote_ranks, pair_size=len(local_ranks) + len(remote_ranks), local_is_first=local_name < remote_name,
+        )
+        if local and remote:
+            st.local_mesh, st.local_placements = local
+            st.remote_mesh, st.remote_placements = remote
+            if not any(isinstance(p, Partial) for p in st.remote_placements):
+                st.m2m_send = plan_m2m(st.local_mesh, st.local_placements, st.remote_mesh, st.remote_placements)
+            if not any(isinstance(p, Partial) for p in st.local_placements):
+                st.m2m_recv = plan_m2m(st.remote_mesh, st.remote_placements, st.local_mesh, st.local_placements)
+        self.pairs[pair] = st
+        self.state.set_matched(pair)
+        logger.info("Agent %s: pair '%s' matched: %s %s <-> %s %s", self.rank, pair, local_name, local_ranks, remote_name, remote_ranks)
+
+    # ---- RegisterTensors --------------------------------------------------------------------------
+    def _register_tensors_job(self, msg: RegisterTensors):
+        from .agent import decode_tensor
+
+        batch_id = msg.batch_id
+        entries = []  # (pair_name, kind, tensor-or-desc)
+        for pair_name, payload in msg.tensors:
+            if pair_name not in self.pairs:
+                raise ValueError(f"RegisterTensors for unknown pair: {pair_name}")
+            kind, obj = decode_tensor(bytes(payload))
+            entries.append((pair_name, kind, obj))
+        pair_names = list(dict.fromkeys(p for p, _, _ in entries))
+        first = self.pairs[pair_names[0]]
+        for p in pair_names[1:]:
+            ps = self.pairs[p]
+            if set(ps.local_ranks) != set(first.local_ranks) or set(ps.remote_ranks) != set(first.remote_ranks):
+                raise ValueError(f"Batch {batch_id}: pair '{p}' spans different ranks than pair '{pair_names[0]}'")
+        kinds = {k for _, k, _ in entries}
+        if len(kinds) != 1:
+            raise ValueError(f"Batch {batch_id}: CPU and CUDA tensors cannot be mixed")
+        kind = kinds.pop()
+        batch = BatchState(batch_id=batch_id, pair_names=pair_names, bucket_size=msg.bucket_size,
+                           local_leader=min(first.local_ranks), local_ranks=list(first.local_ranks),
+                           remote_ranks=list(first.remote_ranks))
+        for p, _, obj in entries:
+            batch.pair_tensors.setdefault(p, []).append(obj)
+        all_ranks = sorted(set(first.local_ranks) | set(first.remote_ranks))
+
+        # publish what the other agents need, then wait for theirs
+        meta = {"rank": self.rank, "kind": kind, "local_name": first.local_name}
+        if kind == "cuda":
+            from ..parallel.peer import PeerMemory
+
+            if self._peer is None:
+                self._peer = PeerMemory(self.device)
+            flags = {d: torch.zeros(len(all_ranks), dtype=torch.int32, device=self.device) for d in ("fwd", "bwd")}
+            batch.keepalive.append(flags)
+            meta["descs"] = [obj for _, _, obj in entries]
+            meta["flags"] = {d: self._peer.describe(t) for d, t in flags.items()}
+            meta["gpu"] = str(torch.cuda.get_device_properties(self.device).uuid)
+        else:
+            meta["descs"] = [(tuple(t.shape), str(t.dtype).replace("torch.", "")) for _, _, t in entries]
+        self.store.set_bytes(f"batch:{batch_id}/rank:{self.rank}/meta", pickle.dumps(meta))
+        metas = {}
+        while len(metas) < len(all_ranks):
+            for r in all_ranks:
+                if r not in metas:
+                    raw = self.store.get_bytes(f"batch:{batch_id}/rank:{r}/meta")
+                    if raw:
+                        metas[r] = pickle.loads(raw)
+            if len(metas) < len(all_ranks):
+                yield
+        for r, m in metas.items():
+            if len(m["descs"]) != len(entries) or m["kind"] != kind:
+                raise ValueError(f"Batch {batch_id}: rank {r} registered {len(m['descs'])} {m['kind']} tensors, "
+                                 f"rank {self.rank} registered {len(entries)} {kind} tensors")
+        if kind == "cuda":
+            self._build_p2p(batch, entries, metas, all_ranks, flags)
+        else:
+            self._build_buckets(batch, entries, metas)
+        self.batches[batch_id] = batch
+        logger.info("Agent %s: batch %s registered (%d tensors, %s)", self.rank, batch_id, len(entries), kind)
+
+    def _build_buckets(self, batch: BatchState, entries, metas) -> None:
+        """CPU tensors: chunks and buckets for both directions (gloo bucket executor)."""
+        import torch as _t
+
+        remote0 = metas[batch.remote_ranks[0]]["descs"]
+        send_chunks, recv_chunks = [], []
+        fallback = True
+        for k, (pair_name, _, t) in enumerate(entries):
+            ps = self.pairs[pair_name]
+            rdtype = getattr(_t, remote0[k][1])
+            if ps.m2m_send is not None:
+                fallback = False
+                send_chunks += m2m_to_chunks(ps.m2m_send, self.rank, source_tensor=t, transfer_dtype=_wire_dtype(t.dtype, rdtype),
+                                             source_mesh=ps.local_mesh, tensor_id=k)
+            if ps.m2m_recv is not None:
+                fallback = False
+                recv_chunks += m2m_to_chunks(ps.m2m_recv, self.rank, target_tensor=t, transfer_dtype=_wire_dtype(rdtype, t.dtype),
+                                             source_mesh=ps.remote_mesh, tensor_id=k)
+        if not fallback:
+            size = batch.bucket_size or 1
+            batch.send_buckets = chunk_to_bucket_ops(send_chunks, size)
+            batch.recv_buckets = chunk_to_bucket_ops(recv_chunks, size)
+        if fallback:
+            batch.send_exec = batch.recv_exec = "plain"
+        else:
+            # a direction is usable only if every pair of the batch has a plan for it (a Partial side can only send)
+            pairs = [self.pairs[p] for p in batch.pair_names]
+            batch.send_exec = "gloo" if all(ps.m2m_send is not None for ps in pairs) else None
+            batch.recv_exec = "gloo" if all(ps.m2m_recv is not None for ps in pairs) else None
+
+    def _build_p2p(self, batch: BatchState, entries, metas, all_ranks, flags) -> None:
+        """CUDA tensors: one copy table per direction, built from every agent's descriptors."""
+        from ..comm.p2p import P2PBatch, PairLayout
+
+        first = self.pairs[batch.pair_names[0]]
+        local_name = first.local_name
+        # canonical direction names so that both sides pick the same flag array for a direction
+        send_dir = "fwd" if first.local_is_first else "bwd"
+        recv_dir = "bwd" if first.local_is_first else "fwd"
+
+        def build(direction: str, sending: bool):
+            layouts, ok = [], True
+            for pair_name, _, _ in entries:
+                ps = self.pairs[pair_name]
+                m = ps.m2m_send if sending else ps.m2m_recv
+                if m is None:
+                    ok = False
+                    break
+                lay = (PairLayout(ps.local_mesh, ps.local_placements, ps.remote_mesh, ps.remote_placements) if sending
+                       else PairLayout(ps.remote_mesh, ps.remote_placements, ps.local_mesh, ps.local_placements))
+                lay._plan = m
+                layouts.append(lay)
+            if not ok:
+                return None
+            src_side = set(batch.local_ranks if sending else batch.remote_ranks)
+            by_rank = {}
+            for r in all_ranks:
+                descs = metas[r]["descs"]
+                by_rank[r] = {
+                    "rank": r,
+                    "src": descs if r in src_side else [None] * len(descs),
+                    "dst": descs if r not in src_side else [None] * len(descs),
+                    "flags": metas[r]["flags"][direction],
+                }
+            b = P2PBatch(self.rank, all_ranks, self.device, peer=self._peer, use_ipc=True)
+            return b.build_from(layouts, by_rank, flags[direction])
+
+        batch.send_exec = build(send_dir, True)
+        batch.recv_exec = build(recv_dir, False)
+        # the device-side wait is used only when no other agent of the batch drives the same physical GPU:
+        # two processes time-slicing one GPU must never have one kernel spin on a flag the other one sets
+        mine = metas[self.rank]["gpu"]
+        batch.keepalive.append({"shared_gpu": sum(1 for r in all_ranks if metas[r]["gpu"] == mine) > 1})
+
+    # ---- Transfer -----------------------------------------------------------------------------------
+    def _store_barrier(self, key_prefix: str, ranks):
+        """All `ranks` set `{key_prefix}/rank:{r}`; yields until every key is there."""
+        self.store.set(f"{key_prefix}/rank:{self.rank}", "1")
+        cands = [f"{key_prefix}/rank:{r}" for r in ranks]
+        while len(self.store.poll_keys(f"{key_prefix}/rank:*", "1", cands)) < len(ranks):
+            yield
+
+    def _transfer_job(self, msg: Transfer):
+        batch = self.batches.get(msg.batch_id)
+        if batch is None:
+            raise ValueError(f"Transfer for unknown batch: {msg.batch_id}")
+        sending = msg.transfer_type == "send"
+        signal_key = f"batch:{batch.batch_id}/state:transfer_signal"
+        if (batch.send_exec if sending else batch.recv_exec) is None:
+            raise RuntimeError(
+                f"Batch {batch.batch_id}: no {msg.transfer_type} plan. That direction has a Partial target, which is "
+                "not supported; Partial is only valid as a source placement."
+            )
+        batch.epoch += 1
+        epoch = batch.epoch
+        if sending and self.rank == batch.local_leader:
+            # the epoch of the newest send is what receivers compare with the receives they have completed; the
+            # "1"/"0" key of the reference is kept for observers but is not what `query_transfer_signal` reads,
+            # because a late "0" of receive k can overwrite the "1" of send k+1
+            self.store.set(f"batch:{batch.batch_id}/state:send_epoch", str(epoch), component="global")
+            self.store.set(signal_key, "1", component="global")
+        all_ranks = sorted(set(batch.local_ranks) | set(batch.remote_ranks))
+        # both sides meet here, like the reference's barrier on the batch group (agent.py:457)
+        yield from self._store_barrier(f"batch:{batch.batch_id}/go:{epoch}", all_ranks)
+
+        ex = batch.send_exec if sending else batch.recv_exec
+        t0 = time.perf_counter()
+        if ex == "gloo":
+            bucket_comm(batch.send_buckets if sending else batch.recv_buckets)
+        elif ex == "plain":
+            yield from self._plain_transfer(batch, sending)
+        else:
+            yield from self._p2p_transfer(batch, ex, sending, epoch)
+        ms = (time.perf_counter() - t0) * 1e3
+        self.state.put(f"batch:{batch.batch_id}/state:last_{msg.transfer_type}_ms", f"{ms:.3f}".encode())
+        if not sending:
+            batch.recv_done = epoch
+            if self.rank == batch.local_leader:
+                self.store.set(signal_key, "0", component="global")
+        logger.info("Agent %s: batch %s %s done in %.2f ms", self.rank, batch.batch_id, msg.transfer_type, ms)
+
+    def _p2p_transfer(self, batch: BatchState, ex, sending: bool, epoch: int):
+        shared_gpu = any(isinstance(k, dict) and k.get("shared_gpu") for k in batch.keepalive)
+        stream = torch.cuda.current_stream(self.device)
+        ex.epoch = epoch - 1
+        ex.begin()
+        done_prefix = f"batch:{batch.batch_id}/done:{epoch}"
+        if sending:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            ex.send(stream)
+            e1.record(stream)
+            while not e1.query():
+                yield
+            ex.check()
+            self.state.put(f"batch:{batch.batch_id}/state:last_send_device_ms", f"{e0.elapsed_time(e1):.3f}".encode())
+            self.store.set(f"{done_prefix}/rank:{self.rank}", "1")
+        else:
+            producers = list(ex._producers)
+            if not shared_gpu:
+                ev = torch.cuda.Event()
+                ex.recv(stream, timeout_s=min(self.store_timeout, 60.0))
+                ev.record(stream)
+                while not ev.query():
+                    yield
+                ex.check()
+            else:
+                cands = [f"{done_prefix}/rank:{r}" for r in producers]
+                while len(self.store.poll_keys(f"{done_prefix}/rank:*", "1", cands)) < len(producers):
+                    yield
+
+    def _plain_transfer(self, batch: BatchState, sending: bool):
+        """No layout was declared: tensor i goes whole to the same-index rank of the other side (reference
+        fallback, src/etha/tensor_bus/agent.py:485-498)."""
+        import torch.distributed as dist
+
+        peer = batch.remote_ranks[sorted(batch.local_ranks).index(self.rank)]
+        works = []
+        for pair_name in batch.pair_names:
+            for t in batch.pair_tensors[pair_name]:
+                works.append(dist.isend(t, dst=peer) if sending else dist.irecv(t, src=peer))
+        for w in works:
+            w.wait()
+        yield
+
+    # ---- QueryStatus / CleanupBatch -----------------------------------------------------------------
+    def _query_status_job(self, msg: QueryStatus):
+        if msg.batch_id not in self.batches:
+            raise ValueError(f"QueryStatus for unknown batch: {msg.batch_id}")
+        if msg.state_name != "transfer_signal":
+            raise ValueError(f"Invalid state name: {msg.state_name}")
+        raw = self.store.try_get(f"batch:{msg.batch_id}/state:send_epoch", component="global")
+        pending = int(raw.decode()) > self.batches[msg.batch_id].recv_done if raw else False
+        self.state.set_signal(msg.batch_id, msg.state_name, pending)
+        return
+        yield
+
+    def _cleanup_batch_job(self, msg: CleanupBatch):
+        if self.batches.pop(msg.batch_id, None) is None:
+            logger.warning("Agent %s: cleanup for unknown batch %s", self.rank, msg.batch_id)
+        return
+        yield

@@ -22,4 +22,5 @@ class BatchState:
     send_buckets: list | None = None
     recv_buckets: list | None = None
     epoch: int = 0
+    recv_done: int = 0  # epoch of the last receive this agent completed
     keepalive: list = field(default_factory=list)
