@@ -1,0 +1,37 @@
+"""The multi-process weight-sync example (agents + trainer workers + inference workers as separate processes),
+the integration test the reference runs on 8 GPUs (tests/test_distributed_model_transfer.py): here on CPU/gloo
+for every run, and on GPUs through CUDA IPC + the peer-to-peer kernels when at least two are present."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LAUNCH = os.path.join(ROOT, "examples", "weight_sync", "launch.py")
+
+
+def _run(*args, timeout=600):
+    proc = subprocess.run([sys.executable, LAUNCH, *args], capture_output=True, text=True, timeout=timeout)
+    out = proc.stdout + proc.stderr
+    assert proc.returncode == 0, out[-4000:]
+    assert "all inference ranks verified their shards" in out
+    return out
+
+
+@pytest.mark.timeout(900)
+def test_example_cpu_two_plus_two():
+    out = _run("--side-size", "2", "--model", "tiny", "--device", "cpu", "--syncs", "2")
+    assert out.count('"golden_match": true') == 4
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.timeout(900)
+def test_example_gpu_peer_to_peer():
+    import torch
+
+    side = 2 if torch.cuda.device_count() >= 4 else 1
+    out = _run("--side-size", str(side), "--model", "tiny", "--syncs", "3", "--source-dtype", "float32")
+    assert out.count('"golden_match": true') == 2 * side
