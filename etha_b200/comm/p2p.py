@@ -133,6 +133,7 @@ class P2PBatch:
         table = CopyTable(self.device, tile_bytes=self.tile_bytes)
         consumers_i_write: set[int] = set()
         producers_i_wait: set[int] = set()
+        self._all_local = True  # every destination lies in this process's memory on this device
         for i, (layout, src, dst) in enumerate(self._entries):
             m2m = layout.plan()
             reductions = list(m2m.source_partial_reductions or [])
@@ -170,6 +171,8 @@ class P2PBatch:
                     if tuple(t_cshape) != tuple(s_cshape):
                         raise ValueError(f"tensor {i}: cell shapes differ, source {s_cshape} vs target {t_cshape} on rank {d.rank}")
                     dsts.append(self.peer.slice_ref(ddesc, cell_slices(d.cell, t_cshape, len(ddesc.shape))))
+                    if ddesc.region.pid != self.peer.pid or ddesc.region.device_index != self.device.index:
+                        self._all_local = False
                     consumers_i_write.add(d.rank)
                 table.add(s_cshape, srcs, dsts, fam.sizes if fam else (), fam.ops if fam else ())
         table.finalize()
@@ -209,7 +212,8 @@ class P2PBatch:
             raise RuntimeError("build() first")
         if self._signals is None and self.table.empty:
             return
-        self.table.launch(stream, self._signals, self.epoch, ctas_per_sm=ctas_per_sm, bulk=bulk)
+        # the TMA kernel is used only when every destination is in this GPU's own memory
+        self.table.launch(stream, self._signals, self.epoch, ctas_per_sm=ctas_per_sm, bulk=bulk and self._all_local)
 
     def recv(self, stream: torch.cuda.Stream | None = None, timeout_s: float = 10.0) -> None:
         """Enqueue the bounded wait for every producer that writes into this rank."""

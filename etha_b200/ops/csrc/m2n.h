@@ -101,11 +101,13 @@ int etha_wait_flags(const uint32_t* flags, const uint32_t* which, uint32_t n, ui
                     uint32_t* status, void* stream);
 int etha_set_flags(const uint64_t* signals, uint32_t n_signals, uint32_t epoch, void* stream);
 
-// TMA (cp.async.bulk) variant for RAW 16-byte ops with a single source; other ops are skipped (returns
-// the number of ops it did not handle in *skipped if non-null).
+// TMA (cp.async.bulk) variant of the fast class for destinations in this GPU's own memory. Every op of the
+// table must satisfy etha_op_bulk_ok (16-byte bit copy, one source, one destination, at most one strided dim
+// whose rows are at least 512 bytes). One warp per CTA; `grid` is normally the SM count.
+int etha_op_bulk_ok(const struct M2NOp* op);
 int etha_m2n_bulk_launch(const struct M2NOp* ops, const uint32_t* tile_start, uint32_t n_ops, int grid,
                          uint32_t* sync_scratch, const uint64_t* signals, uint32_t n_signals, uint32_t epoch,
-                         void* stream);
+                         int do_signal, void* stream);
 
 // ---- IPC / device helpers ---------------------------------------------------------------------
 int etha_ipc_export(uint64_t ptr, unsigned char* handle64, uint64_t* base, uint64_t* size);

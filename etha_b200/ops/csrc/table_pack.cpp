@@ -49,6 +49,12 @@ int etha_op_class(const M2NOp* op) {
   return (op->mode == M2N_MODE_RAW && op->unit_bytes_src == 16 && op->ndim <= 1) ? 0 : 1;
 }
 
+int etha_op_bulk_ok(const M2NOp* op) {
+  if (etha_op_class(op) != 0 || op->nsrc != 1 || op->ndst != 1 || (op->flags & M2N_FLAG_MULTIMEM)) return 0;
+  if (op->ndim == 1 && (uint64_t)op->inner_units * 16 < 512) return 0;
+  return 1;
+}
+
 uint32_t etha_op_tiles(const M2NOp* op) {
   if (op->total_units == 0) return 0;
   return (op->total_units + op->tile_units - 1) / op->tile_units;

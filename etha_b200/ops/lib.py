@@ -63,6 +63,8 @@ def cuda_lib() -> C.CDLL:
         lib.etha_op_tiles.restype = u32
         lib.etha_op_class.argtypes = [vp]
         lib.etha_op_class.restype = i32
+        lib.etha_op_bulk_ok.argtypes = [vp]
+        lib.etha_op_bulk_ok.restype = i32
         lib.etha_m2n_launch.argtypes = [vp, vp, u32, i32, i32, i32, vp, vp, u32, u32, i32, vp]
         lib.etha_m2n_launch.restype = i32
         lib.etha_set_flags.argtypes = [vp, u32, u32, vp]

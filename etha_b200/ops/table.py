@@ -63,6 +63,7 @@ class CopyTable:
         self._keepalive: list = []
         self.n_ops = [0, 0]
         self.n_tiles = [0, 0]
+        self.bulk_ok = True  # every fast-class op may go through the TMA kernel (local destinations only)
 
     # ---- building ---------------------------------------------------------------------------
     def add(
@@ -125,6 +126,8 @@ class CopyTable:
                 tiles = self._lib.etha_op_tiles(buf)
                 if tiles:
                     cls = self._lib.etha_op_class(buf)
+                    if cls == 0 and not self._lib.etha_op_bulk_ok(buf):
+                        self.bulk_ok = False
                     self._packed.append((cls, tiles, buf.raw))
                 mult = 1 if not multimem else 1
                 self.payload_bytes += numel * ddtype.itemsize * len(part) * mult
@@ -196,7 +199,7 @@ class CopyTable:
         for c in classes:
             last = c == classes[-1]
             grid = min(self.n_tiles[c], self.sm_count * ctas_per_sm)
-            if bulk and c == 0 and hasattr(self._lib, "etha_m2n_bulk_launch"):
+            if bulk and c == 0 and self.bulk_ok:
                 rc = self._lib.etha_m2n_bulk_launch(
                     self._ops_dev[c].data_ptr(), self._tiles_dev[c].data_ptr(), self.n_ops[c],
                     min(self.n_tiles[c], self.sm_count), self._sync.data_ptr(), sig_ptr, n_sig if last else 0,

@@ -168,3 +168,43 @@ def test_local_copy_helper():
     ops.local_copy(a, b)
     torch.cuda.synchronize()
     assert torch.equal(b, a.to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("shape,cols", [((4096, 4096), None), ((2048, 4096), (1024, 2048)), ((777, 1024), None), ((64, 8192), (256, 4352))])
+def test_tma_bulk_kernel_matches_ldst(shape, cols):
+    src = _rand(shape, torch.bfloat16, 21)
+    sv = src if cols is None else src[:, cols[0]:cols[1]]
+    dst = torch.zeros(sv.shape, dtype=torch.bfloat16, device=DEV)
+    flags = torch.zeros(2, dtype=torch.int32, device=DEV)
+    addrs = torch.tensor([flags.data_ptr() + 4], dtype=torch.int64, device=DEV)
+    t = CopyTable(DEV)
+    t.add_copy(sv, dst)
+    t.finalize()
+    assert t.bulk_ok
+    for epoch in (1, 2):
+        dst.zero_()
+        t.launch(signals=addrs, epoch=epoch, bulk=True)
+        torch.cuda.synchronize()
+        assert t.error_word() == 0 and flags.tolist() == [0, epoch]
+        assert torch.equal(dst, sv)
+
+
+def test_tma_bulk_many_ops_and_fallback():
+    srcs = [_rand((512 + 64 * i, 2048), torch.bfloat16, 30 + i) for i in range(9)]
+    dsts = [torch.zeros_like(s) for s in srcs]
+    t = CopyTable(DEV)
+    for s, d in zip(srcs, dsts):
+        t.add_copy(s, d)
+    t.finalize()
+    t.launch(bulk=True)
+    torch.cuda.synchronize()
+    assert t.bulk_ok and all(torch.equal(s, d) for s, d in zip(srcs, dsts))
+    # a fan-out op is not eligible: the table quietly uses the LD/ST kernel
+    a, b1, b2 = _rand((256, 256), torch.float32, 40), torch.zeros(256, 256, device=DEV), torch.zeros(256, 256, device=DEV)
+    t2 = CopyTable(DEV)
+    t2.add((256, 256), [SliceRef.of(a)], [SliceRef.of(b1), SliceRef.of(b2)])
+    t2.finalize()
+    assert not t2.bulk_ok
+    t2.launch(bulk=True)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b1) and torch.equal(a, b2)
