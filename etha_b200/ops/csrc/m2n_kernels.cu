@@ -59,6 +59,14 @@ __device__ __forceinline__ uint8_t ld_stream<uint8_t>(const void* p) {
   return (uint8_t)v;
 }
 
+// a thread that reads 32 contiguous bytes with two 16-byte loads touches every 32-byte sector twice: let the
+// first load allocate the sector in L1 so that the second one does not go back to L2
+__device__ __forceinline__ uint4 ld_keep(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
 template <typename V>
 __device__ __forceinline__ void st_plain(void* p, V v) {
   *reinterpret_cast<V*>(p) = v;
@@ -113,10 +121,20 @@ struct Elem;
 
 template <>
 struct Elem<M2N_F32> {
-  static __device__ __forceinline__ void load8(const char* p, float (&f)[8]) {
-    uint4 a = ld_stream<uint4>(p), b = ld_stream<uint4>(p + 16);
+  static constexpr int W = 2;  // 16-byte words per 8 elements
+  static __device__ __forceinline__ void load_raw(const char* p, uint4 (&r)[2]) {
+    r[0] = ld_keep(p);
+    r[1] = ld_keep(p + 16);
+  }
+  static __device__ __forceinline__ void decode(const uint4 (&r)[2], float (&f)[8]) {
+    const uint4 a = r[0], b = r[1];
     f[0] = __uint_as_float(a.x), f[1] = __uint_as_float(a.y), f[2] = __uint_as_float(a.z), f[3] = __uint_as_float(a.w);
     f[4] = __uint_as_float(b.x), f[5] = __uint_as_float(b.y), f[6] = __uint_as_float(b.z), f[7] = __uint_as_float(b.w);
+  }
+  static __device__ __forceinline__ void load8(const char* p, float (&f)[8]) {
+    uint4 r[2];
+    load_raw(p, r);
+    decode(r, f);
   }
   static __device__ __forceinline__ void store8(char* p, const float (&f)[8]) {
     st_plain<uint4>(p, make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3])));
@@ -129,10 +147,17 @@ struct Elem<M2N_F32> {
 template <>
 struct Elem<M2N_BF16> {
   static __device__ __forceinline__ float up(uint32_t w, int hi) { return __uint_as_float(hi ? (w & 0xffff0000u) : (w << 16)); }
-  static __device__ __forceinline__ void load8(const char* p, float (&f)[8]) {
-    uint4 a = ld_stream<uint4>(p);
+  static constexpr int W = 1;
+  static __device__ __forceinline__ void load_raw(const char* p, uint4 (&r)[1]) { r[0] = ld_stream<uint4>(p); }
+  static __device__ __forceinline__ void decode(const uint4 (&r)[1], float (&f)[8]) {
+    const uint4 a = r[0];
     f[0] = up(a.x, 0), f[1] = up(a.x, 1), f[2] = up(a.y, 0), f[3] = up(a.y, 1);
     f[4] = up(a.z, 0), f[5] = up(a.z, 1), f[6] = up(a.w, 0), f[7] = up(a.w, 1);
+  }
+  static __device__ __forceinline__ void load8(const char* p, float (&f)[8]) {
+    uint4 r[1];
+    load_raw(p, r);
+    decode(r, f);
   }
   static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -152,9 +177,16 @@ struct Elem<M2N_F16> {
     float2 f = __half22float2(h);
     lo = f.x, hi = f.y;
   }
-  static __device__ __forceinline__ void load8(const char* p, float (&f)[8]) {
-    uint4 a = ld_stream<uint4>(p);
+  static constexpr int W = 1;
+  static __device__ __forceinline__ void load_raw(const char* p, uint4 (&r)[1]) { r[0] = ld_stream<uint4>(p); }
+  static __device__ __forceinline__ void decode(const uint4 (&r)[1], float (&f)[8]) {
+    const uint4 a = r[0];
     unpack(a.x, f[0], f[1]), unpack(a.y, f[2], f[3]), unpack(a.z, f[4], f[5]), unpack(a.w, f[6], f[7]);
+  }
+  static __device__ __forceinline__ void load8(const char* p, float (&f)[8]) {
+    uint4 r[1];
+    load_raw(p, r);
+    decode(r, f);
   }
   static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
     __half2 v = __floats2half2_rn(lo, hi);
@@ -177,6 +209,13 @@ __device__ __forceinline__ float reduce2(float a, float b, int op) {
     case M2N_PROD: return a * b;
     default: return a + b;  // SUM and AVG
   }
+}
+
+template <int DT>
+__device__ __forceinline__ float round_through(float x) {
+  if constexpr (DT == M2N_BF16) return __bfloat162float(__float2bfloat16_rn(x));
+  if constexpr (DT == M2N_F16) return __half2float(__float2half_rn(x));
+  return x;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -217,17 +256,62 @@ __device__ __forceinline__ void tile_raw(const M2NOp& op, uint32_t base, uint32_
 
 template <int SDT, int DDT, int UNROLL>
 __device__ __forceinline__ void tile_cvt8(const M2NOp& op, uint32_t base, uint32_t limit) {
+  // all loads of the thread are issued before the first store, so UNROLL * 16..32 bytes are in flight per thread
   const char* src = reinterpret_cast<const char*>(op.src[0]);
+  uint4 raw[UNROLL][Elem<SDT>::W];
+  int64_t doff[UNROLL];
+  bool ok[UNROLL];
 #pragma unroll
   for (int u = 0; u < UNROLL; ++u) {
     uint32_t unit = base + u * blockDim.x + threadIdx.x;
-    if (unit < limit) {
-      int64_t so, dof;
-      unit_offsets(op, unit, so, dof);
-      float f[8];
-      Elem<SDT>::load8(src + so, f);
-      for (int j = 0; j < op.ndst; ++j) Elem<DDT>::store8(reinterpret_cast<char*>(op.dst[j]) + dof, f);
+    ok[u] = unit < limit;
+    if (ok[u]) {
+      int64_t so;
+      unit_offsets(op, unit, so, doff[u]);
+      Elem<SDT>::load_raw(src + so, raw[u]);
     }
+  }
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    if (ok[u]) {
+      float f[8];
+      Elem<SDT>::decode(raw[u], f);
+      for (int j = 0; j < op.ndst; ++j) Elem<DDT>::store8(reinterpret_cast<char*>(op.dst[j]) + doff[u], f);
+    }
+  }
+}
+
+// Single-level Partial collapse of exactly NSRC sources, 8 elements per unit: every source word of the unit is
+// requested before the first one is used.
+template <int SDT, int DDT, int NSRC>
+__device__ __forceinline__ void tile_reduce_flat(const M2NOp& op, uint32_t base, uint32_t limit, int unroll) {
+  const int rop = op.red_op[0];
+  for (int u = 0; u < unroll; ++u) {
+    uint32_t unit = base + u * blockDim.x + threadIdx.x;
+    if (unit >= limit) continue;
+    int64_t so, dof;
+    unit_offsets(op, unit, so, dof);
+    uint4 raw[NSRC][Elem<SDT>::W];
+#pragma unroll
+    for (int i = 0; i < NSRC; ++i) Elem<SDT>::load_raw(reinterpret_cast<const char*>(op.src[i]) + so, raw[i]);
+    float acc[8];
+    Elem<SDT>::decode(raw[0], acc);
+#pragma unroll
+    for (int i = 1; i < NSRC; ++i) {
+      float f[8];
+      Elem<SDT>::decode(raw[i], f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = reduce2(acc[k], f[k], rop);
+    }
+    if (rop == M2N_AVG) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = __fdiv_rn(acc[k], (float)NSRC);
+    }
+    if constexpr (SDT != DDT) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = round_through<SDT>(acc[k]);
+    }
+    for (int j = 0; j < op.ndst; ++j) Elem<DDT>::store8(reinterpret_cast<char*>(op.dst[j]) + dof, acc);
   }
 }
 
@@ -244,13 +328,6 @@ __device__ __forceinline__ void tile_cvt1(const M2NOp& op, uint32_t base, uint32
       for (int j = 0; j < op.ndst; ++j) Elem<DDT>::store1(reinterpret_cast<char*>(op.dst[j]) + dof, f);
     }
   }
-}
-
-template <int DT>
-__device__ __forceinline__ float round_through(float x) {
-  if constexpr (DT == M2N_BF16) return __bfloat162float(__float2bfloat16_rn(x));
-  if constexpr (DT == M2N_F16) return __half2float(__float2half_rn(x));
-  return x;
 }
 
 // Partial collapse: level 0 groups of red_size[0] consecutive sources, then level 1 over the group results;
@@ -306,20 +383,37 @@ __device__ __forceinline__ void tile_reduce(const M2NOp& op, uint32_t base, uint
   }
 }
 
-template <int UNROLL>
+// One out-of-line walker per (source dtype, destination dtype): each gets its own register allocation.
+constexpr int kTypedUnroll = 2;
+
+template <int S, int D>
+__device__ __noinline__ void walk_cvt(const M2NOp& op, uint32_t base, uint32_t limit) {
+  const uint32_t step = blockDim.x * kTypedUnroll;
+  if (op.unit_elems == 8) {
+    for (uint32_t b = base; b < limit; b += step) tile_cvt8<S, D, kTypedUnroll>(op, b, limit);
+  } else {
+    for (uint32_t b = base; b < limit; b += step) tile_cvt1<S, D, kTypedUnroll>(op, b, limit);
+  }
+}
+
+template <int S, int D>
+__device__ __noinline__ void walk_red(const M2NOp& op, uint32_t base, uint32_t limit) {
+  const bool vec = op.unit_elems == 8;
+  const bool flat = vec && op.red_size[1] == 1;
+  const uint32_t step = blockDim.x * 2;
+  for (uint32_t b = base; b < limit; b += step) {
+    if (flat && op.nsrc == 2) tile_reduce_flat<S, D, 2>(op, b, limit, 2);
+    else if (flat && op.nsrc == 4) tile_reduce_flat<S, D, 4>(op, b, limit, 2);
+    else if (flat && op.nsrc == 8) tile_reduce_flat<S, D, 8>(op, b, limit, 2);
+    else if (vec) tile_reduce<S, D, 8>(op, b, limit, 2);
+    else tile_reduce<S, D, 1>(op, b, limit, 2);
+  }
+}
+
 __device__ __forceinline__ bool dispatch_typed(const M2NOp& op, uint32_t base, uint32_t limit) {
   const int key = (op.mode << 8) | (op.src_dtype << 4) | op.dst_dtype;
-  const bool vec = op.unit_elems == 8;
-#define CASE_CVT(S, D)                                                   \
-  case (M2N_MODE_CVT << 8) | (S << 4) | D:                               \
-    if (vec) tile_cvt8<S, D, UNROLL>(op, base, limit);                   \
-    else tile_cvt1<S, D, UNROLL>(op, base, limit);                       \
-    return true;
-#define CASE_RED(S, D)                                                   \
-  case (M2N_MODE_REDUCE << 8) | (S << 4) | D:                            \
-    if (vec) tile_reduce<S, D, 8>(op, base, limit, UNROLL);              \
-    else tile_reduce<S, D, 1>(op, base, limit, UNROLL);                  \
-    return true;
+#define CASE_CVT(S, D) case (M2N_MODE_CVT << 8) | (S << 4) | D: walk_cvt<S, D>(op, base, limit); return true;
+#define CASE_RED(S, D) case (M2N_MODE_REDUCE << 8) | (S << 4) | D: walk_red<S, D>(op, base, limit); return true;
   switch (key) {
     CASE_CVT(M2N_F32, M2N_BF16) CASE_CVT(M2N_F32, M2N_F16) CASE_CVT(M2N_BF16, M2N_F32) CASE_CVT(M2N_F16, M2N_F32)
     CASE_CVT(M2N_BF16, M2N_F16) CASE_CVT(M2N_F16, M2N_BF16)
@@ -402,13 +496,8 @@ template <typename V>
 __device__ __noinline__ void walk_raw(const M2NOp& op, uint32_t base, uint32_t limit) {
   for (uint32_t b = base; b < limit; b += blockDim.x * kGenUnroll) tile_raw<V, kGenUnroll, -1>(op, b, limit);
 }
-__device__ __noinline__ bool walk_typed(const M2NOp& op, uint32_t base, uint32_t limit) {
-  for (uint32_t b = base; b < limit; b += blockDim.x * kGenUnroll)
-    if (!dispatch_typed<kGenUnroll>(op, b, limit)) return false;
-  return true;
-}
 
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, 3)
 m2n_general_kernel(const M2NOp* __restrict__ ops, const uint32_t* __restrict__ tile_start, uint32_t n_ops,
                    uint32_t* sync, const uint64_t* __restrict__ signals, uint32_t n_signals, uint32_t epoch,
                    int do_signal) {
@@ -428,7 +517,7 @@ m2n_general_kernel(const M2NOp* __restrict__ ops, const uint32_t* __restrict__ t
         case 2: walk_raw<uint16_t>(op, base, limit); break;
         default: walk_raw<uint8_t>(op, base, limit); break;
       }
-    } else if (!walk_typed(op, base, limit)) {
+    } else if (!dispatch_typed(op, base, limit)) {
       if (threadIdx.x == 0) sync[1] = M2N_BAD_OP;
     }
   }

@@ -198,7 +198,8 @@ class CopyTable:
             return
         for c in classes:
             last = c == classes[-1]
-            grid = min(self.n_tiles[c], self.sm_count * ctas_per_sm)
+            # the general kernel is compiled for three 256-thread CTAs per SM, the fast one for two of 512
+            grid = min(self.n_tiles[c], self.sm_count * (ctas_per_sm if c == 0 else max(ctas_per_sm, 3)))
             if bulk and c == 0 and self.bulk_ok:
                 rc = self._lib.etha_m2n_bulk_launch(
                     self._ops_dev[c].data_ptr(), self._tiles_dev[c].data_ptr(), self.n_ops[c],
