@@ -78,6 +78,7 @@ class P2PBatch:
         peer: PeerMemory | None = None,
         tile_bytes: int = DEFAULT_TILE_BYTES,
         use_ipc: bool | None = None,
+        nvls=None,
     ):
         self.rank = rank
         self.ranks = list(ranks)
@@ -86,6 +87,10 @@ class P2PBatch:
         self.peer = peer or PeerMemory(self.device)
         self.use_ipc = (len(self.ranks) > 1) if use_ipc is None else use_ipc
         self.tile_bytes = tile_bytes
+        # optional `NvlsTeam`: routes whose consumers are exactly the team, at one common arena offset, are written
+        # with one multicast store instead of one store per replica
+        self.nvls = nvls
+        self.multicast_ops = 0
         self._entries: list[tuple[PairLayout, torch.Tensor | None, torch.Tensor | None]] = []
         self.table: CopyTable | None = None
         self.epoch = 0
@@ -174,7 +179,8 @@ class P2PBatch:
                     if ddesc.region.pid != self.peer.pid or ddesc.region.device_index != self.device.index:
                         self._all_local = False
                     consumers_i_write.add(d.rank)
-                table.add(s_cshape, srcs, dsts, fam.sizes if fam else (), fam.ops if fam else ())
+                if not self._add_multicast(table, s_cshape, srcs, route, by_rank, i, dsts):
+                    table.add(s_cshape, srcs, dsts, fam.sizes if fam else (), fam.ops if fam else ())
         table.finalize()
         self.table = table
         # flags: slot k of a consumer's flag array belongs to producer ranks[k]
@@ -191,6 +197,34 @@ class P2PBatch:
             if self._producers else None
         )
         self._built = True
+
+    def _add_multicast(self, table, shape, srcs, route, by_rank, i, dsts) -> bool:
+        """Try to serve a fan-out route through the NVLS team; False means "use one store per replica"."""
+        team = self.nvls
+        if team is None or len(srcs) != 1 or len(dsts) < 2:
+            return False
+        if {d.rank for d in route.dsts} != set(getattr(team, "replicas", None) or team.ranks):
+            return False
+        descs = [by_rank[d.rank]["dst"][i] for d in route.dsts]
+        if any(dd.region.handle != b"vmm" for dd in descs):
+            return False
+        # same offset inside every member's arena, same strides and dtype: one multicast address serves all
+        offs = set()
+        for d, ref, dd in zip(route.dsts, dsts, descs):
+            base = self.peer.map_region(dd.region)
+            offs.add((ref.ptr - base, ref.strides, ref.dtype))
+        if len(offs) != 1 or srcs[0].dtype != dsts[0].dtype:
+            return False
+        off, strides, dtype = next(iter(offs))
+        from ..ops.table import SliceRef
+
+        mc = SliceRef(team.mc_va + off, strides, dtype, team.mc_va, team.mc_va + team.arena.size)
+        try:
+            table.add(shape, srcs, [mc], multimem=True)
+        except ValueError:
+            return False  # not a 16-byte aligned bit copy: the packer refuses, fall back
+        self.multicast_ops += 1
+        return True
 
     # ---- execution -----------------------------------------------------------------------
     @property

@@ -70,11 +70,18 @@ class PeerMemory:
         self._exported: dict[int, RegionDesc] = {}  # base -> desc
         self._mapped: dict[tuple, int] = {}  # region key -> local base
         self._keepalive: list[torch.Tensor] = []
+        self._arenas: list = []  # VMM arenas of this process: their views are described without an IPC handle
 
     # ---- owner side -----------------------------------------------------------------------
+    def register_arena(self, arena) -> None:
+        self._arenas.append(arena)
+
     def describe(self, t: torch.Tensor, keepalive: bool = True) -> TensorDesc:
         if not t.is_cuda:
             raise ValueError("only CUDA tensors can be exported")
+        for arena in self._arenas:
+            if arena.va <= t.data_ptr() < arena.va + arena.size:
+                return arena.describe(t)
         with torch.cuda.device(t.device):
             handle = C.create_string_buffer(64)
             base, size = C.c_uint64(), C.c_uint64()
@@ -104,14 +111,19 @@ class PeerMemory:
             return region.base
         local = self._mapped.get(region.key)
         if local is None:
-            if not region.handle:
-                raise ValueError("region of another process was exported without an IPC handle")
+            if not region.handle or region.handle == b"vmm":
+                raise ValueError("region of another process has no IPC handle and no adopted mapping")
             with torch.cuda.device(self.device):
                 out = C.c_uint64()
                 L.check(self._lib.etha_ipc_open(region.handle, C.byref(out)), "ipc_open")
             local = out.value
             self._mapped[region.key] = local
         return local
+
+    def adopt_mapping(self, region_key: tuple, local_base: int) -> None:
+        """Register a mapping made elsewhere (a VMM arena imported from a file descriptor): descriptors whose
+        region has this `(pid, device_index, base)` key resolve to `local_base`."""
+        self._mapped[tuple(region_key)] = int(local_base)
 
     def slice_ref(self, desc: TensorDesc, index: tuple[slice, ...] = ()) -> SliceRef:
         """`SliceRef` of `tensor[index]` (unit-step slices) for the tensor described by `desc`."""
@@ -124,6 +136,6 @@ class PeerMemory:
 
     def close(self) -> None:
         for local in self._mapped.values():
-            self._lib.etha_ipc_close(local)
+            self._lib.etha_ipc_close(local)  # mappings adopted from elsewhere are unknown to it and left alone
         self._mapped.clear()
         self._keepalive.clear()
