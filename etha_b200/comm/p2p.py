@@ -179,7 +179,7 @@ class P2PBatch:
                     if ddesc.region.pid != self.peer.pid or ddesc.region.device_index != self.device.index:
                         self._all_local = False
                     consumers_i_write.add(d.rank)
-                if not self._add_multicast(table, s_cshape, srcs, route, by_rank, i, dsts):
+                if not self._add_multicast(table, s_cshape, srcs, route, by_rank, i, dsts, fam):
                     table.add(s_cshape, srcs, dsts, fam.sizes if fam else (), fam.ops if fam else ())
         table.finalize()
         self.table = table
@@ -198,10 +198,10 @@ class P2PBatch:
         )
         self._built = True
 
-    def _add_multicast(self, table, shape, srcs, route, by_rank, i, dsts) -> bool:
+    def _add_multicast(self, table, shape, srcs, route, by_rank, i, dsts, fam=None) -> bool:
         """Try to serve a fan-out route through the NVLS team; False means "use one store per replica"."""
         team = self.nvls
-        if team is None or len(srcs) != 1 or len(dsts) < 2:
+        if team is None or len(dsts) < 2:
             return False
         if {d.rank for d in route.dsts} != set(getattr(team, "replicas", None) or team.ranks):
             return False
@@ -213,14 +213,14 @@ class P2PBatch:
         for d, ref, dd in zip(route.dsts, dsts, descs):
             base = self.peer.map_region(dd.region)
             offs.add((ref.ptr - base, ref.strides, ref.dtype))
-        if len(offs) != 1 or srcs[0].dtype != dsts[0].dtype:
+        if len(offs) != 1:
             return False
         off, strides, dtype = next(iter(offs))
         from ..ops.table import SliceRef
 
         mc = SliceRef(team.mc_va + off, strides, dtype, team.mc_va, team.mc_va + team.arena.size)
         try:
-            table.add(shape, srcs, [mc], multimem=True)
+            table.add(shape, srcs, [mc], fam.sizes if fam else (), fam.ops if fam else (), multimem=True)
         except ValueError:
             return False  # not a 16-byte aligned bit copy: the packer refuses, fall back
         self.multicast_ops += 1

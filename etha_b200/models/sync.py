@@ -85,6 +85,8 @@ class WeightSync:
         partial_scale: bool = True,
         extra: Sequence[tuple[torch.Tensor | None, torch.Tensor | None]] = (),
         tile_bytes: int | None = None,
+        nvls: bool = False,
+        nvls_tag: str = "ws",
     ):
         self.model, self.rank, self.device, self.seed = model, rank, torch.device(device), seed
         self.smesh, self.tmesh = mesh_tensor_of(source_mesh), mesh_tensor_of(target_mesh)
@@ -120,11 +122,35 @@ class WeightSync:
             self.dst_arena.buffer.zero_()
             for k, e in enumerate(self.entries):
                 e.target = self.dst_arena.view(k, t_shapes[k], target_dtype)
+        # NVLS: parameters that every consumer holds in full live in a VMM arena bound to one multicast object, so
+        # a producer writes all replicas with one store; every rank of the job is a team member (producers bind an
+        # equally sized scratch arena, see etha_b200.parallel.arena)
+        self.team = None
+        peer = None
+        if nvls:
+            from ..parallel.arena import NvlsTeam, VmmArena
+            from ..parallel.peer import PeerMemory
+
+            rep = [k for k, e in enumerate(self.entries) if all(isinstance(p, Replicate) for p in e.layout.target_placements)]
+            offs, cur = {}, 0
+            for k in rep:
+                offs[k] = cur
+                cur += _align(nbytes(self.entries[k].spec.shape, target_dtype))
+            if cur:
+                peer = PeerMemory(self.device)
+                self.rep_arena = VmmArena(cur, self.device, n_team=len(ranks))
+                self.team = NvlsTeam(rank, list(ranks), self.rep_arena, nvls_tag, exchange, peer=peer)
+                self.team.replicas = self.tmesh.reshape(-1).tolist()
+                if self.is_target:
+                    for k in rep:
+                        t = self.rep_arena.tensor(offs[k], self.entries[k].spec.shape, target_dtype)
+                        t.zero_()
+                        self.entries[k].target = t
         if fill and self.is_source:
             self.fill_sources(partial_scale)
 
         kw = {} if tile_bytes is None else {"tile_bytes": tile_bytes}
-        self.batch = P2PBatch(rank, ranks, self.device, exchange=exchange, **kw)
+        self.batch = P2PBatch(rank, ranks, self.device, exchange=exchange, peer=peer, nvls=self.team, **kw)
         for e in self.entries:
             self.batch.add(e.layout, e.source, e.target)
         for layout, s, t in extra:
@@ -192,3 +218,11 @@ class WeightSync:
 
     def check(self) -> None:
         self.batch.check()
+
+    def close(self) -> None:
+        """Release the multicast team and its arena (call on every rank before exit when `nvls=True`)."""
+        if self.team is not None:
+            torch.cuda.synchronize(self.device)
+            self.team.close()
+            self.rep_arena.close()
+            self.team = None

@@ -202,6 +202,22 @@ struct Elem<M2N_F16> {
   static __device__ __forceinline__ void store1(char* p, float f) { *reinterpret_cast<__half*>(p) = __float2half_rn(f); }
 };
 
+// store 8 converted elements either with plain stores or, for an NVLS destination, with multicast stores
+template <int DDT>
+__device__ __forceinline__ void store8_to(char* p, const float (&f)[8], bool multicast) {
+  if (!multicast) {
+    Elem<DDT>::store8(p, f);
+    return;
+  }
+  if constexpr (DDT == M2N_F32) {
+    st_multimem16(p, make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3])));
+    st_multimem16(p + 16, make_uint4(__float_as_uint(f[4]), __float_as_uint(f[5]), __float_as_uint(f[6]), __float_as_uint(f[7])));
+  } else {
+    st_multimem16(p, make_uint4(Elem<DDT>::pack(f[0], f[1]), Elem<DDT>::pack(f[2], f[3]), Elem<DDT>::pack(f[4], f[5]),
+                                Elem<DDT>::pack(f[6], f[7])));
+  }
+}
+
 __device__ __forceinline__ float reduce2(float a, float b, int op) {
   switch (op) {
     case M2N_MAX: return (a != a) ? a : ((b != b) ? b : fmaxf(a, b));  // NaN propagates, like torch.maximum
@@ -276,7 +292,8 @@ __device__ __forceinline__ void tile_cvt8(const M2NOp& op, uint32_t base, uint32
     if (ok[u]) {
       float f[8];
       Elem<SDT>::decode(raw[u], f);
-      for (int j = 0; j < op.ndst; ++j) Elem<DDT>::store8(reinterpret_cast<char*>(op.dst[j]) + doff[u], f);
+      const bool mc = op.flags & M2N_FLAG_MULTIMEM;
+      for (int j = 0; j < op.ndst; ++j) store8_to<DDT>(reinterpret_cast<char*>(op.dst[j]) + doff[u], f, mc);
     }
   }
 }
@@ -311,7 +328,8 @@ __device__ __forceinline__ void tile_reduce_flat(const M2NOp& op, uint32_t base,
 #pragma unroll
       for (int k = 0; k < 8; ++k) acc[k] = round_through<SDT>(acc[k]);
     }
-    for (int j = 0; j < op.ndst; ++j) Elem<DDT>::store8(reinterpret_cast<char*>(op.dst[j]) + dof, acc);
+    const bool mc = op.flags & M2N_FLAG_MULTIMEM;
+    for (int j = 0; j < op.ndst; ++j) store8_to<DDT>(reinterpret_cast<char*>(op.dst[j]) + dof, acc, mc);
   }
 }
 
@@ -375,7 +393,7 @@ __device__ __forceinline__ void tile_reduce(const M2NOp& op, uint32_t base, uint
     for (int j = 0; j < op.ndst; ++j) {
       char* d = reinterpret_cast<char*>(op.dst[j]) + dof;
       if constexpr (N == 8) {
-        Elem<DDT>::store8(d, acc);
+        store8_to<DDT>(d, acc, op.flags & M2N_FLAG_MULTIMEM);
       } else {
         Elem<DDT>::store1(d, acc[0]);
       }

@@ -138,8 +138,10 @@ int etha_pack_op(const M2NOpSpec* s, M2NOp* o, char* err, int err_len) {
     ubd = unit_elems * ed;
     inner_units = inner_elems / unit_elems;
   }
-  if ((s->flags & M2N_FLAG_MULTIMEM) && !(mode == M2N_MODE_RAW && ubs == 16 && s->ndst == 1))
-    return error(err, err_len, -10, "multicast store needs a 16-byte aligned bit copy with one (multicast) destination");
+  // a multicast destination is written 16 bytes at a time: bit copies in 16-byte units, typed ops in 8-element units
+  if ((s->flags & M2N_FLAG_MULTIMEM) &&
+      !(s->ndst == 1 && ((mode == M2N_MODE_RAW && ubs == 16) || (mode != M2N_MODE_RAW && unit_elems == 8))))
+    return error(err, err_len, -10, "multicast store needs 16-byte aligned units and one (multicast) destination");
 
   int64_t total = inner_units;
   for (auto& d : dims) {
