@@ -95,6 +95,7 @@ def main():
     ap.add_argument("--min-mb", type=int, default=1)
     ap.add_argument("--nvls", type=int, default=0)
     ap.add_argument("--verify", type=int, default=1)
+    ap.add_argument("--layouts", default="S0->S1,S0->R,R->S0", help="comma-separated subset for --config single")
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers (0: full model)")
     args = ap.parse_args()
     rank, world, _ = init_dist(args.gpus)
@@ -129,6 +130,8 @@ def main():
             rows = max(rows // (8 * k) * (8 * k), 8 * k)
             nbytes = rows * 4096 * 2
             for lname, (sp, tp) in layouts.items():
+                if lname not in args.layouts.split(","):
+                    continue
                 model = ModelSpec("one", [TensorSpec("w", (rows, 4096), "column")])
                 # busiest GPU: S0->S1 and R->S0 move B/k per GPU; S0->R delivers B to every consumer
                 busiest = nbytes if lname == "S0->R" else nbytes / k

@@ -143,6 +143,7 @@ class P2PBatch:
             m2m = layout.plan()
             reductions = list(m2m.source_partial_reductions or [])
             smesh = mesh_tensor_of(layout.source_mesh)
+            mine = []
             for route in m2m.routes:
                 if not route.dsts:
                     continue
@@ -150,8 +151,17 @@ class P2PBatch:
                 for d in route.dsts:
                     if d.rank == self.rank:
                         producers_i_wait.add(primary)
-                if primary != self.rank:
-                    continue
+                if primary == self.rank:
+                    mine.append(route)
+            # Producers walk their table in order, so if every producer served consumer 0 first, then consumer 1, ...
+            # all of them would pour into the same GPU at the same time and share its ingress.  Rotate: producer
+            # number p starts with consumer p, then p+1, ... (a permutation schedule over the NVSwitch).
+            s_ranks, t_ranks = layout.source_ranks, layout.target_ranks
+            if self.rank in s_ranks and len(t_ranks) > 1:
+                p, nt = s_ranks.index(self.rank), len(t_ranks)
+                mine.sort(key=lambda r: min((t_ranks.index(d.rank) - p) % nt for d in r.dsts))
+            for route in mine:
+                primary = route.src.rank
                 sdesc = by_rank[primary]["src"][i]
                 if sdesc is None:
                     raise ValueError(f"rank {primary} registered no source for tensor {i}")
