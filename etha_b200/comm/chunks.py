@@ -19,7 +19,7 @@ import torch
 
 from .ir import Chunk, M2MMap, PartialFamily, Transport, partial_family
 
-__all__ = ["m2m_to_chunks", "cell_slices", "padded_slicers", "chunk_shape_of"]
+__all__ = ["m2m_to_chunks", "cell_slices", "padded_slicers", "chunk_shape_of", "plan_fits_shapes"]
 
 
 def padded_slicers(num_slicers: Sequence[int], ndim: int) -> list[int]:
@@ -38,6 +38,24 @@ def chunk_shape_of(shape: Sequence[int], slicers: Sequence[int]) -> tuple[int, .
                 "uneven shards need the shape-aware planner (plan_for_shapes)"
             )
     return tuple(n // k for n, k in zip(shape, slicers))
+
+
+def plan_fits_shapes(m2m: M2MMap, source_shapes: dict, target_shapes: dict) -> bool:
+    """True if the lcm plan applies: every rank's local shape divides into its cells and all cells have one shape.
+
+    Every rank must take this decision from the shapes of ALL ranks of both sides, otherwise a producer whose own
+    shard happens to divide evenly and a consumer whose shard does not would pick different plans."""
+    cell = None
+    for shapes, slicers in ((source_shapes, m2m.source_num_slicers), (target_shapes, m2m.target_num_slicers)):
+        for shape in shapes.values():
+            try:
+                c = chunk_shape_of(shape, padded_slicers(slicers, len(shape)))
+            except ValueError:
+                return False
+            if cell is not None and tuple(c) != tuple(cell):
+                return False
+            cell = c
+    return True
 
 
 def cell_slices(cell: Sequence[int], cshape: Sequence[int], ndim: int) -> tuple[slice, ...]:

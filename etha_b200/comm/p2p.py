@@ -41,6 +41,7 @@ class PairLayout:
     source_placements: Sequence
     target_mesh: Any
     target_placements: Sequence
+    global_shape: Sequence[int] | None = None  # set it (or leave it to be inferred) for unevenly sharded tensors
     _plan: M2MMap | None = None
 
     def plan(self) -> M2MMap:
@@ -140,34 +141,24 @@ class P2PBatch:
         producers_i_wait: set[int] = set()
         self._all_local = True  # every destination lies in this process's memory on this device
         for i, (layout, src, dst) in enumerate(self._entries):
-            m2m = layout.plan()
-            reductions = list(m2m.source_partial_reductions or [])
             smesh = mesh_tensor_of(layout.source_mesh)
+            reductions, transfers = self._transfers_of(layout, i, by_rank)
             mine = []
-            for route in m2m.routes:
-                if not route.dsts:
-                    continue
-                primary = route.src.rank
-                for d in route.dsts:
-                    if d.rank == self.rank:
+            for primary, s_index, cshape, dst_list in transfers:
+                for d_rank, _ in dst_list:
+                    if d_rank == self.rank:
                         producers_i_wait.add(primary)
                 if primary == self.rank:
-                    mine.append(route)
+                    mine.append((primary, s_index, cshape, dst_list))
             # Producers walk their table in order, so if every producer served consumer 0 first, then consumer 1, ...
             # all of them would pour into the same GPU at the same time and share its ingress.  Rotate: producer
             # number p starts with consumer p, then p+1, ... (a permutation schedule over the NVSwitch).
             s_ranks, t_ranks = layout.source_ranks, layout.target_ranks
             if self.rank in s_ranks and len(t_ranks) > 1:
                 p, nt = s_ranks.index(self.rank), len(t_ranks)
-                mine.sort(key=lambda r: min((t_ranks.index(d.rank) - p) % nt for d in r.dsts))
-            for route in mine:
-                primary = route.src.rank
+                mine.sort(key=lambda t: min((t_ranks.index(r) - p) % nt for r, _ in t[3]))
+            for primary, s_index, cshape, dst_list in mine:
                 sdesc = by_rank[primary]["src"][i]
-                if sdesc is None:
-                    raise ValueError(f"rank {primary} registered no source for tensor {i}")
-                s_slicers = padded_slicers(m2m.source_num_slicers, len(sdesc.shape))
-                s_cshape = chunk_shape_of(sdesc.shape, s_slicers)
-                s_index = cell_slices(route.src.cell, s_cshape, len(sdesc.shape))
                 fam = partial_family(smesh, reductions, primary) if reductions else None
                 members = fam.ranks if fam is not None else (primary,)
                 srcs = []
@@ -177,20 +168,14 @@ class P2PBatch:
                         raise ValueError(f"Partial contributor {q} of tensor {i} has no matching shard")
                     srcs.append(self.peer.slice_ref(qdesc, s_index))
                 dsts = []
-                for d in route.dsts:
-                    ddesc = by_rank[d.rank]["dst"][i]
-                    if ddesc is None:
-                        raise ValueError(f"rank {d.rank} registered no target for tensor {i}")
-                    t_slicers = padded_slicers(m2m.target_num_slicers, len(ddesc.shape))
-                    t_cshape = chunk_shape_of(ddesc.shape, t_slicers)
-                    if tuple(t_cshape) != tuple(s_cshape):
-                        raise ValueError(f"tensor {i}: cell shapes differ, source {s_cshape} vs target {t_cshape} on rank {d.rank}")
-                    dsts.append(self.peer.slice_ref(ddesc, cell_slices(d.cell, t_cshape, len(ddesc.shape))))
+                for d_rank, d_index in dst_list:
+                    ddesc = by_rank[d_rank]["dst"][i]
+                    dsts.append(self.peer.slice_ref(ddesc, d_index))
                     if ddesc.region.pid != self.peer.pid or ddesc.region.device_index != self.device.index:
                         self._all_local = False
-                    consumers_i_write.add(d.rank)
-                if not self._add_multicast(table, s_cshape, srcs, route, by_rank, i, dsts, fam):
-                    table.add(s_cshape, srcs, dsts, fam.sizes if fam else (), fam.ops if fam else ())
+                    consumers_i_write.add(d_rank)
+                if not self._add_multicast(table, cshape, srcs, [r for r, _ in dst_list], by_rank, i, dsts, fam):
+                    table.add(cshape, srcs, dsts, fam.sizes if fam else (), fam.ops if fam else ())
         table.finalize()
         self.table = table
         # flags: slot k of a consumer's flag array belongs to producer ranks[k]
@@ -208,19 +193,60 @@ class P2PBatch:
         )
         self._built = True
 
-    def _add_multicast(self, table, shape, srcs, route, by_rank, i, dsts, fam=None) -> bool:
+    def _transfers_of(self, layout: "PairLayout", i: int, by_rank: dict[int, dict]):
+        """Normalised transfer list of tensor `i`: `(primary, source slices, box shape, [(consumer, slices), ...])`.
+
+        Evenly divisible shards use the shape-independent lcm plan; anything else (or a layout that names its
+        global shape) uses the explicit-box plan of `etha_b200.comm.shaped`."""
+        s_ranks, t_ranks = layout.source_ranks, layout.target_ranks
+        s_shapes = {r: tuple(by_rank[r]["src"][i].shape) for r in s_ranks if by_rank[r]["src"][i] is not None}
+        t_shapes = {r: tuple(by_rank[r]["dst"][i].shape) for r in t_ranks if by_rank[r]["dst"][i] is not None}
+        if len(s_shapes) != len(s_ranks) or len(t_shapes) != len(t_ranks):
+            missing = [r for r in s_ranks if r not in s_shapes] + [r for r in t_ranks if r not in t_shapes]
+            raise ValueError(f"tensor {i}: ranks {missing} registered no tensor for their side")
+        m2m = layout.plan()
+        out = []
+        even = layout.global_shape is None
+        if even:
+            try:
+                for route in m2m.routes:
+                    if not route.dsts:
+                        continue
+                    sshape = s_shapes[route.src.rank]
+                    s_cshape = chunk_shape_of(sshape, padded_slicers(m2m.source_num_slicers, len(sshape)))
+                    dst_list = []
+                    for d in route.dsts:
+                        tshape = t_shapes[d.rank]
+                        t_cshape = chunk_shape_of(tshape, padded_slicers(m2m.target_num_slicers, len(tshape)))
+                        if tuple(t_cshape) != tuple(s_cshape):
+                            raise ValueError(f"tensor {i}: cell shapes differ, source {s_cshape} vs target {t_cshape}")
+                        dst_list.append((d.rank, cell_slices(d.cell, t_cshape, len(tshape))))
+                    out.append((route.src.rank, cell_slices(route.src.cell, s_cshape, len(sshape)), tuple(s_cshape), dst_list))
+                return list(m2m.source_partial_reductions or []), out
+            except ValueError:
+                out = []  # uneven shards: fall through to the explicit-box plan
+        from .shaped import infer_global_shape, plan_for_shape
+
+        gshape = layout.global_shape or infer_global_shape(layout.source_mesh, layout.source_placements, s_shapes)
+        plan = plan_for_shape(layout.source_mesh, layout.source_placements, layout.target_mesh, layout.target_placements, gshape)
+        sl = lambda box: tuple(slice(a, b) for a, b in box)
+        for r in plan.routes:
+            out.append((r.src_rank, sl(r.src_box), r.shape, [(d, sl(box)) for d, box in r.dsts]))
+        return plan.source_partial_reductions, out
+
+    def _add_multicast(self, table, shape, srcs, dst_ranks, by_rank, i, dsts, fam=None) -> bool:
         """Try to serve a fan-out route through the NVLS team; False means "use one store per replica"."""
         team = self.nvls
         if team is None or len(dsts) < 2:
             return False
-        if {d.rank for d in route.dsts} != set(getattr(team, "replicas", None) or team.ranks):
+        if set(dst_ranks) != set(getattr(team, "replicas", None) or team.ranks):
             return False
-        descs = [by_rank[d.rank]["dst"][i] for d in route.dsts]
+        descs = [by_rank[r]["dst"][i] for r in dst_ranks]
         if any(dd.region.handle != b"vmm" for dd in descs):
             return False
         # same offset inside every member's arena, same strides and dtype: one multicast address serves all
         offs = set()
-        for d, ref, dd in zip(route.dsts, dsts, descs):
+        for ref, dd in zip(dsts, descs):
             base = self.peer.map_region(dd.region)
             offs.add((ref.ptr - base, ref.strides, ref.dtype))
         if len(offs) != 1:

@@ -177,23 +177,38 @@ class AgentHandlers:
             rdtype = getattr(_t, remote0[k][1])
             if ps.m2m_send is not None:
                 fallback = False
-                send_chunks += m2m_to_chunks(ps.m2m_send, self.rank, source_tensor=t, transfer_dtype=_wire_dtype(t.dtype, rdtype),
-                                             source_mesh=ps.local_mesh, tensor_id=k)
+                send_chunks += self._chunks_for(ps.m2m_send, ps.local_mesh, ps.local_placements, ps.remote_mesh,
+                                                ps.remote_placements, {r: metas[r]["descs"][k][0] for r in ps.local_ranks},
+                                                {r: metas[r]["descs"][k][0] for r in ps.remote_ranks}, source=t, wire=_wire_dtype(t.dtype, rdtype), k=k)
             if ps.m2m_recv is not None:
                 fallback = False
-                recv_chunks += m2m_to_chunks(ps.m2m_recv, self.rank, target_tensor=t, transfer_dtype=_wire_dtype(rdtype, t.dtype),
-                                             source_mesh=ps.remote_mesh, tensor_id=k)
-        if not fallback:
-            size = batch.bucket_size or 1
-            batch.send_buckets = chunk_to_bucket_ops(send_chunks, size)
-            batch.recv_buckets = chunk_to_bucket_ops(recv_chunks, size)
+                recv_chunks += self._chunks_for(ps.m2m_recv, ps.remote_mesh, ps.remote_placements, ps.local_mesh,
+                                                ps.local_placements, {r: metas[r]["descs"][k][0] for r in ps.remote_ranks},
+                                                {r: metas[r]["descs"][k][0] for r in ps.local_ranks}, target=t, wire=_wire_dtype(rdtype, t.dtype), k=k)
         if fallback:
             batch.send_exec = batch.recv_exec = "plain"
         else:
+            size = batch.bucket_size or 1
+            batch.send_buckets = chunk_to_bucket_ops(send_chunks, size)
+            batch.recv_buckets = chunk_to_bucket_ops(recv_chunks, size)
             # a direction is usable only if every pair of the batch has a plan for it (a Partial side can only send)
             pairs = [self.pairs[p] for p in batch.pair_names]
             batch.send_exec = "gloo" if all(ps.m2m_send is not None for ps in pairs) else None
             batch.recv_exec = "gloo" if all(ps.m2m_recv is not None for ps in pairs) else None
+
+    def _chunks_for(self, m2m, smesh, splc, tmesh, tplc, source_shapes, target_shapes, source=None, target=None,
+                    wire=None, k=0):
+        """Chunks of one tensor: the lcm plan when every shard of both sides divides evenly, explicit boxes otherwise
+        (decided from all ranks' shapes, so both sides agree)."""
+        from ..comm.chunks import plan_fits_shapes
+
+        if plan_fits_shapes(m2m, source_shapes, target_shapes):
+            return m2m_to_chunks(m2m, self.rank, source_tensor=source, target_tensor=target, transfer_dtype=wire,
+                                 source_mesh=smesh, tensor_id=k)
+        from ..comm.shaped import infer_global_shape, plan_for_shape, shaped_to_chunks
+
+        plan = plan_for_shape(smesh, splc, tmesh, tplc, infer_global_shape(smesh, splc, source_shapes))
+        return shaped_to_chunks(plan, self.rank, source, target, wire, source_mesh=smesh, tensor_id=k)
 
     def _build_p2p(self, batch: BatchState, entries, metas, all_ranks, flags) -> None:
         """CUDA tensors: one copy table per direction, built from every agent's descriptors."""

@@ -5,7 +5,7 @@ import math
 
 import pytest
 import torch
-from torch.distributed.tensor.placement_types import Partial, Replicate
+from torch.distributed.tensor.placement_types import Partial, Replicate, Shard
 
 from etha_b200.comm.baselines import local_slice_of
 from etha_b200.comm.p2p import P2PBatch, PairLayout, link_local
@@ -76,6 +76,19 @@ def test_reshard_matrix_disjoint(case):
 @pytest.mark.parametrize("case", CASES_8, ids=[str(i) for i in range(len(CASES_8))])
 def test_reshard_matrix_overlapping(case):
     _run_case(case, overlap=True)
+
+
+UNEVEN = [
+    ((2,), (Shard(0),), (2,), (Shard(1),), (1000, 333), False),
+    ((2,), (Shard(0),), (2,), (Shard(1),), (7, 4096), False),
+    ((2, 2), (Shard(0), Shard(1)), (3,), (Shard(0),), (10, 7), False),
+    ((2,), (Partial(),), (2,), (Shard(0),), (5, 3), False),
+]
+
+
+@pytest.mark.parametrize("case", UNEVEN, ids=[str(i) for i in range(len(UNEVEN))])
+def test_uneven_shards(case):
+    _run_case(case, overlap=False)
 
 
 @pytest.mark.parametrize("sd,td", [(torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32), (torch.bfloat16, torch.bfloat16)])

@@ -19,7 +19,8 @@ from etha_b200.tensor_bus.client import TensorBusClient, TensorBusError
 
 from dist_utils import free_port, run_distributed
 
-SHAPES = [(1024, 512), (512, 1024), (2048, 256), (256, 2048), (1000, 334), (8, 4096), (128, 128), (64, 64)]
+# includes the unevenly sharded shapes (1000 x 333 over 2 column shards, 7 rows over 2 row shards)
+SHAPES = [(1024, 512), (512, 1024), (2048, 256), (256, 2048), (1000, 333), (7, 4096), (128, 128), (64, 64)]
 
 
 def _start_agent(rank, world, port, tag, tmp):
