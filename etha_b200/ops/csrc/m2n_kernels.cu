@@ -270,7 +270,7 @@ __device__ __forceinline__ void tile_raw(const M2NOp& op, uint32_t base, uint32_
   }
 }
 
-template <int SDT, int DDT, int UNROLL>
+template <int SDT, int DDT, int UNROLL, int ND = -1>
 __device__ __forceinline__ void tile_cvt8(const M2NOp& op, uint32_t base, uint32_t limit) {
   // all loads of the thread are issued before the first store, so UNROLL * 16..32 bytes are in flight per thread
   const char* src = reinterpret_cast<const char*>(op.src[0]);
@@ -283,7 +283,7 @@ __device__ __forceinline__ void tile_cvt8(const M2NOp& op, uint32_t base, uint32
     ok[u] = unit < limit;
     if (ok[u]) {
       int64_t so;
-      unit_offsets(op, unit, so, doff[u]);
+      unit_offsets<ND>(op, unit, so, doff[u]);
       Elem<SDT>::load_raw(src + so, raw[u]);
     }
   }
@@ -300,14 +300,14 @@ __device__ __forceinline__ void tile_cvt8(const M2NOp& op, uint32_t base, uint32
 
 // Single-level Partial collapse of exactly NSRC sources, 8 elements per unit: every source word of the unit is
 // requested before the first one is used.
-template <int SDT, int DDT, int NSRC>
+template <int SDT, int DDT, int NSRC, int ND = -1>
 __device__ __forceinline__ void tile_reduce_flat(const M2NOp& op, uint32_t base, uint32_t limit, int unroll) {
   const int rop = op.red_op[0];
   for (int u = 0; u < unroll; ++u) {
     uint32_t unit = base + u * blockDim.x + threadIdx.x;
     if (unit >= limit) continue;
     int64_t so, dof;
-    unit_offsets(op, unit, so, dof);
+    unit_offsets<ND>(op, unit, so, dof);
     uint4 raw[NSRC][Elem<SDT>::W];
 #pragma unroll
     for (int i = 0; i < NSRC; ++i) Elem<SDT>::load_raw(reinterpret_cast<const char*>(op.src[i]) + so, raw[i]);
@@ -408,7 +408,14 @@ template <int S, int D>
 __device__ __noinline__ void walk_cvt(const M2NOp& op, uint32_t base, uint32_t limit) {
   const uint32_t step = blockDim.x * kTypedUnroll;
   if (op.unit_elems == 8) {
-    for (uint32_t b = base; b < limit; b += step) tile_cvt8<S, D, kTypedUnroll>(op, b, limit);
+    // boxes that are one run or rows of a matrix (almost every weight) skip the generic index arithmetic
+    if (op.ndim == 0) {
+      for (uint32_t b = base; b < limit; b += step) tile_cvt8<S, D, kTypedUnroll, 0>(op, b, limit);
+    } else if (op.ndim == 1) {
+      for (uint32_t b = base; b < limit; b += step) tile_cvt8<S, D, kTypedUnroll, 1>(op, b, limit);
+    } else {
+      for (uint32_t b = base; b < limit; b += step) tile_cvt8<S, D, kTypedUnroll>(op, b, limit);
+    }
   } else {
     for (uint32_t b = base; b < limit; b += step) tile_cvt1<S, D, kTypedUnroll>(op, b, limit);
   }
@@ -420,7 +427,9 @@ __device__ __noinline__ void walk_red(const M2NOp& op, uint32_t base, uint32_t l
   const bool flat = vec && op.red_size[1] == 1;
   const uint32_t step = blockDim.x * 2;
   for (uint32_t b = base; b < limit; b += step) {
-    if (flat && op.nsrc == 2) tile_reduce_flat<S, D, 2>(op, b, limit, 2);
+    if (flat && op.nsrc == 2 && op.ndim == 0) tile_reduce_flat<S, D, 2, 0>(op, b, limit, 2);
+    else if (flat && op.nsrc == 2 && op.ndim == 1) tile_reduce_flat<S, D, 2, 1>(op, b, limit, 2);
+    else if (flat && op.nsrc == 2) tile_reduce_flat<S, D, 2>(op, b, limit, 2);
     else if (flat && op.nsrc == 4) tile_reduce_flat<S, D, 4>(op, b, limit, 2);
     else if (flat && op.nsrc == 8) tile_reduce_flat<S, D, 8>(op, b, limit, 2);
     else if (vec) tile_reduce<S, D, 8>(op, b, limit, 2);
