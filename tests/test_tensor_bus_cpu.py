@@ -146,3 +146,38 @@ def test_command_without_agent_times_out(tmp_path):
         c.transfer("b", "send", blocking=True, timeout=0.3)  # nobody ever posts the semaphore
     c.command_queue.close(destroy=True)
     s.close()
+
+
+def _absent_peer_worker(rank, world, port, tag, tmp):
+    """Only rank 0's worker ever declares the pair: the other side never shows up (an agent whose worker died
+    before init_pair).  The waiting agent gives up after its store timeout, reports it, and keeps serving."""
+    store = TorchTCPStore("127.0.0.1", port, world_size=world, is_master=(rank == 0), timeout=60.0,
+                          wait_for_workers=True, namespace=tag)
+    cq, st = f"{tmp}/{tag}_r{rank}_command.lmdb", f"{tmp}/{tag}_r{rank}_state.lmdb"
+    agent = TensorBusAgent(rank, world, "127.0.0.1", port, cq, st, store_timeout=1.0, store_namespace=tag, store=store,
+                           device="cpu")
+    th = threading.Thread(target=agent.run, daemon=True)
+    th.start()
+    client = TensorBusClient(rank, cq, st, connection_timeout=10.0)
+    try:
+        if rank == 0:
+            t0 = time.monotonic()
+            with pytest.raises(TensorBusError, match="did not complete within"):
+                client.init_pair("lonely", "trainer", "inference", 1, torch.tensor([0]), (Shard(0),), timeout=20.0)
+            assert 0.9 < time.monotonic() - t0 < 10.0
+            assert client.state.matched("lonely") is None
+            # the agent is still alive and answers the next command
+            with pytest.raises(TensorBusError, match="unknown batch"):
+                client.transfer("nope", "recv", blocking=True, timeout=10.0)
+            assert client.state.heartbeat_age() < 2.0
+    finally:
+        dist.barrier()
+        agent.stop()
+        th.join(timeout=5)
+        client.close()
+        agent.command_queue.close(destroy=True)
+        agent.state.close()
+
+
+def test_peer_that_never_registers_times_out_cleanly(tmp_path):
+    run_distributed(_absent_peer_worker, 2, free_port(), "t" + uuid.uuid4().hex[:6], str(tmp_path))
