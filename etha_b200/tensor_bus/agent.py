@@ -139,7 +139,9 @@ class TensorBusAgent(AgentHandlers):
         """Serve commands until `stop()`; `max_idle_s` ends the loop after that long without any command (tests)."""
         last = time.monotonic()
         while not self._stop.is_set():
-            busy = self.step(block_s=TIME_INTERVAL)
+            # idle: block on the queue semaphore for a tick; with jobs in flight poll fast, a transfer's barrier and
+            # completion are a handful of store round trips and should not pay a millisecond sleep each
+            busy = self.step(block_s=TIME_INTERVAL if not self._jobs else 0.00005)
             if busy:
                 last = time.monotonic()
             elif max_idle_s is not None and time.monotonic() - last > max_idle_s:
