@@ -402,7 +402,13 @@ __device__ __forceinline__ void tile_reduce(const M2NOp& op, uint32_t base, uint
 }
 
 // One out-of-line walker per (source dtype, destination dtype): each gets its own register allocation.
-constexpr int kTypedUnroll = 2;
+#ifndef ETHA_TYPED_UNROLL
+#define ETHA_TYPED_UNROLL 2
+#endif
+#ifndef ETHA_GENERAL_CTAS
+#define ETHA_GENERAL_CTAS 3
+#endif
+constexpr int kTypedUnroll = ETHA_TYPED_UNROLL;
 
 template <int S, int D>
 __device__ __noinline__ void walk_cvt(const M2NOp& op, uint32_t base, uint32_t limit) {
@@ -524,7 +530,7 @@ __device__ __noinline__ void walk_raw(const M2NOp& op, uint32_t base, uint32_t l
   for (uint32_t b = base; b < limit; b += blockDim.x * kGenUnroll) tile_raw<V, kGenUnroll, -1>(op, b, limit);
 }
 
-__global__ void __launch_bounds__(256, 3)
+__global__ void __launch_bounds__(256, ETHA_GENERAL_CTAS)
 m2n_general_kernel(const M2NOp* __restrict__ ops, const uint32_t* __restrict__ tile_start, uint32_t n_ops,
                    uint32_t* sync, const uint64_t* __restrict__ signals, uint32_t n_signals, uint32_t epoch,
                    int do_signal) {
@@ -600,6 +606,9 @@ inline int fail(cudaError_t e, const char* what) {
 }  // namespace
 
 extern "C" {
+
+// resident 256-thread CTAs per SM the general kernel was compiled for (the launcher sizes its grid with it)
+int etha_general_ctas_per_sm(void) { return ETHA_GENERAL_CTAS; }
 
 int etha_m2n_launch(const M2NOp* ops, const uint32_t* tile_start, uint32_t n_ops, int typed, int grid, int block,
                     uint32_t* sync_scratch, const uint64_t* signals, uint32_t n_signals, uint32_t epoch,

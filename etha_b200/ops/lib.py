@@ -3,6 +3,7 @@
 from __future__ import annotations
 
 import ctypes as C
+import os
 import threading
 
 from . import build
@@ -52,7 +53,8 @@ def cuda_lib() -> C.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
-        path = build.build_cuda_lib()
+        # ETHA_CUDA_LIB selects a pre-built library (e.g. one compiled with other tuning macros)
+        path = os.environ.get("ETHA_CUDA_LIB") or build.build_cuda_lib()
         lib = C.CDLL(path, mode=C.RTLD_GLOBAL)
         vp, u32, u64, i32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int
         lib.etha_last_error.restype = C.c_char_p
@@ -63,6 +65,7 @@ def cuda_lib() -> C.CDLL:
         lib.etha_op_tiles.restype = u32
         lib.etha_op_class.argtypes = [vp]
         lib.etha_op_class.restype = i32
+        lib.etha_general_ctas_per_sm.restype = i32
         lib.etha_op_bulk_ok.argtypes = [vp]
         lib.etha_op_bulk_ok.restype = i32
         lib.etha_m2n_launch.argtypes = [vp, vp, u32, i32, i32, i32, vp, vp, u32, u32, i32, vp]

@@ -198,8 +198,9 @@ class CopyTable:
             return
         for c in classes:
             last = c == classes[-1]
-            # the general kernel is compiled for three 256-thread CTAs per SM, the fast one for two of 512
-            grid = min(self.n_tiles[c], self.sm_count * (ctas_per_sm if c == 0 else max(ctas_per_sm, 3)))
+            # the fast kernel is compiled for two 512-thread CTAs per SM; the general one reports its own occupancy
+            per_sm = ctas_per_sm if c == 0 else max(ctas_per_sm, self._lib.etha_general_ctas_per_sm())
+            grid = min(self.n_tiles[c], self.sm_count * per_sm)
             if bulk and c == 0 and self.bulk_ok:
                 rc = self._lib.etha_m2n_bulk_launch(
                     self._ops_dev[c].data_ptr(), self._tiles_dev[c].data_ptr(), self.n_ops[c],

@@ -36,6 +36,7 @@ def main() -> int:
     ap.add_argument("--syncs", type=int, default=3)
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"])
     ap.add_argument("--source-dtype", default="bfloat16")
+    ap.add_argument("--share-gpu", action="store_true", help="run every agent and worker on GPU 0 (several ranks per GPU)")
     ap.add_argument("--timeout", type=float, default=600.0)
     args = ap.parse_args()
     n = args.side_size
@@ -49,7 +50,7 @@ def main() -> int:
         procs.append((tag, subprocess.Popen([sys.executable, *argv], env=env)))
 
     for r in range(world):
-        env = dict(base, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r if args.device == "cuda" else 0),
+        env = dict(base, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r if args.device == "cuda" and not args.share_gpu else 0),
                    MASTER_PORT=str(master_port))
         argv = ["-m", "etha_b200.tensor_bus.agent_main", "--store-port", str(store_port), "--path-prefix", prefix]
         if args.device == "cpu":
@@ -57,7 +58,7 @@ def main() -> int:
         spawn(f"agent{r}", argv, env)
     for role, offset in (("trainer", 0), ("inference", n)):
         for r in range(n):
-            env = dict(base, RANK=str(r), WORLD_SIZE=str(n), LOCAL_RANK=str(r + offset if args.device == "cuda" else 0),
+            env = dict(base, RANK=str(r), WORLD_SIZE=str(n), LOCAL_RANK=str(r + offset if args.device == "cuda" and not args.share_gpu else 0),
                        AGENT_RANK_OFFSET=str(offset))
             spawn(f"{role}{r}", [os.path.join(HERE, "worker.py"), "--role", role, "--model", args.model, "--side-size", str(n),
                                  "--syncs", str(args.syncs), "--path-prefix", prefix, "--device", args.device,

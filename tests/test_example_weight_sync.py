@@ -35,3 +35,12 @@ def test_example_gpu_peer_to_peer():
     side = 2 if torch.cuda.device_count() >= 4 else 1
     out = _run("--side-size", str(side), "--model", "tiny", "--syncs", "3", "--source-dtype", "float32")
     assert out.count('"golden_match": true') == 2 * side
+
+
+@pytest.mark.gpu
+@pytest.mark.timeout(900)
+def test_example_two_agents_sharing_one_gpu():
+    """Producer and consumer agents (and their workers) all on GPU 0: NCCL cannot run two ranks on one device, the
+    peer-to-peer path can; completion then goes through the KV store, never through a device-side spin."""
+    out = _run("--side-size", "1", "--model", "tiny", "--syncs", "3", "--share-gpu")
+    assert out.count('"golden_match": true') == 2
