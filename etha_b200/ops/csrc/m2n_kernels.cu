@@ -403,10 +403,10 @@ __device__ __forceinline__ void tile_reduce(const M2NOp& op, uint32_t base, uint
 
 // One out-of-line walker per (source dtype, destination dtype): each gets its own register allocation.
 #ifndef ETHA_TYPED_UNROLL
-#define ETHA_TYPED_UNROLL 2
+#define ETHA_TYPED_UNROLL 4
 #endif
 #ifndef ETHA_GENERAL_CTAS
-#define ETHA_GENERAL_CTAS 3
+#define ETHA_GENERAL_CTAS 4
 #endif
 constexpr int kTypedUnroll = ETHA_TYPED_UNROLL;
 
