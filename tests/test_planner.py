@@ -143,3 +143,47 @@ def test_partial_family_order():
     assert fam.ranks == (0, 3, 1, 4, 2, 5) and fam.sizes == (2, 3) and fam.ops == ("sum", "max")
     fam = partial_family(torch.arange(4).view(2, 2), [(1, "sum")], 2)
     assert fam.ranks == (2, 3)
+
+
+# ---- property test: random meshes and placements against the DTensor-arithmetic oracle -------------------
+from hypothesis import given, settings  # noqa: E402
+from hypothesis import strategies as st  # noqa: E402
+
+_mesh_shape = st.lists(st.integers(1, 3), min_size=1, max_size=3).filter(lambda s: math.prod(s) <= 8)
+
+
+def _placements(n, allow_partial):
+    kinds = [st.just(Replicate()), st.builds(Shard, st.integers(0, 2))]
+    if allow_partial:
+        kinds.append(st.sampled_from([Partial(), Partial("max")]))
+    return st.lists(st.one_of(*kinds), min_size=n, max_size=n).map(tuple)
+
+
+@settings(max_examples=120, deadline=None)
+@given(st.data())
+def test_random_layouts_match_dtensor_arithmetic(data):
+    ss = tuple(data.draw(_mesh_shape))
+    ts = tuple(data.draw(_mesh_shape))
+    sp = data.draw(_placements(len(ss), True))
+    tp = data.draw(_placements(len(ts), False))
+    ns, nt = math.prod(ss), math.prod(ts)
+    overlap = data.draw(st.booleans())
+    smesh = torch.arange(ns).view(ss)
+    tmesh = torch.arange(0 if overlap else ns, (0 if overlap else ns) + nt).view(ts)
+    m = plan_m2m(smesh, sp, tmesh, tp)
+    table, grid, sc, tc = oracle_routes(smesh, sp, tmesh, tp)
+    got = {(r.src.rank, r.src.cell): sorted((d.rank, d.cell) for d in r.dsts) for r in m.routes if r.dsts}
+    assert got == {k: sorted(v) for k, v in table.items()}
+    assert m.source_num_slicers == [g // c for g, c in zip(grid, sc)]
+    # every consumer cell is delivered exactly once
+    delivered = [(d.rank, d.cell) for r in m.routes for d in r.dsts]
+    assert len(delivered) == len(set(delivered)) == nt * math.prod(m.target_num_slicers)
+    # reduce-only entries exist exactly for the other members of a Partial family
+    if any(isinstance(p, Partial) for p in sp):
+        red = [(i, p.reduce_op) for i, p in enumerate(sp) if isinstance(p, Partial)]
+        for r in [r for r in m.routes if r.dsts]:
+            fam = partial_family(smesh, red, r.src.rank)
+            for q in fam.ranks:
+                assert any(x.src.rank == q and x.src.cell == r.src.cell for x in m.routes)
+    else:
+        assert all(r.dsts for r in m.routes)
