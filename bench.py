@@ -18,7 +18,6 @@ import argparse
 import json
 import os
 import sys
-import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
@@ -39,6 +38,7 @@ def parse_args():
     p.add_argument("--tile-kb", type=int, default=64)
     p.add_argument("--bucket-mb", type=int, default=256, help="reference arm: bucket size in MiB (0 = one message per chunk)")
     p.add_argument("--no-verify", action="store_true")
+    p.add_argument("--bus", type=int, default=1, help="also time the sync through agents + TensorBusClient (0 to skip)")
     return p.parse_args()
 
 
@@ -205,6 +205,11 @@ def run_ours(args) -> dict:
     stamp_errors = int(max_over_ranks(float(stamp_errors), world))
     e2e_gbps = ws.payload_bytes / (e2e_ms * 1e-3) / 1e9
 
+    # ---- the same sync through the tensor bus: agents as separate processes, workers use TensorBusClient ----------
+    bus = None
+    if args.bus:
+        bus = run_bus_e2e(args, rank, world, dev, ws, smesh, tmesh, stamp_src, stamp_dst, is_src, is_dst)
+
     result = {
         "metric": METRIC,
         "value": round(gbps, 2),
@@ -241,12 +246,82 @@ def run_ours(args) -> dict:
                     "every consumer reads stamp + wait status back to pinned memory and the host checks them",
             "stamp_errors": stamp_errors,
         },
+        "e2e_bus": bus,
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
     if group is not None:
         dist.destroy_process_group()
     return result if rank == 0 else {}
+
+
+def run_bus_e2e(args, rank, world, dev, ws, smesh, tmesh, stamp_src, stamp_dst, is_src, is_dst) -> dict:
+    """End to end through the public bus API: one agent process per GPU (two on the single GPU of N=1), this
+    process attaches with TensorBusClient, registers the same shards and times transfer("send"|"recv") rounds.
+    A failure here never invalidates the numbers above: it is reported in the returned dict."""
+    import torch
+    import torch.distributed as dist
+
+    from etha_b200.models.bus_sync import BusItem, bus_roundtrip
+    from torch.distributed.tensor.placement_types import Replicate
+
+    steps = max(3, min(args.steps, 10))
+    pin_in = torch.zeros(16, dtype=torch.int64).pin_memory()
+    pin_out = torch.zeros(16, dtype=torch.int64).pin_memory()
+    errors = [0]
+    stream = torch.cuda.current_stream()
+
+    def on_step(k, phase):
+        if phase == "before_send":
+            pin_in.fill_(k)
+            stamp_src.copy_(pin_in, non_blocking=True)
+            stream.synchronize()  # the agent reads the stamp from another process: it must have landed
+        else:
+            pin_out.copy_(stamp_dst, non_blocking=True)
+            stream.synchronize()
+            if int(pin_out[0]) != k:
+                errors[0] += 1
+
+    def share(obj):
+        if world == 1:
+            return obj
+        box = [obj]
+        dist.broadcast_object_list(box, src=0, device=torch.device("cpu"))
+        return box[0]
+
+    items = [BusItem(e.source, e.target, tuple(e.layout.source_placements), tuple(e.layout.target_placements)) for e in ws.entries]
+    items.append(BusItem(stamp_src, stamp_dst, (Replicate(),), (Replicate(),)))
+    src_agents = smesh.tolist() if world > 1 else [0]
+    dst_agents = tmesh.tolist() if world > 1 else [1]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def stop():
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    out, failure = None, None
+    try:
+        out = bus_roundtrip(rank, world, dev.index, items, src_agents, dst_agents, steps=steps, warmup=2, share=share,
+                            on_step=on_step, timeout=150.0, timer=(e0.record, stop))
+    except Exception as e:  # reported, not fatal
+        failure = f"{type(e).__name__}: {e}"[:300]
+    ms = max_over_ranks(out["ms_per_step"] if out else float("inf"), world)
+    bad = int(max_over_ranks(float(errors[0]), world))
+    if ms == float("inf"):
+        return {"unavailable": failure or "another rank failed"}
+    return {
+        "value": round(ws.payload_bytes / (ms * 1e-3) / 1e9, 2),
+        "unit": "GB/s",
+        "ms_per_step": round(ms, 4),
+        "steps": steps,
+        "agent_send_device_ms_last": out.get("agent_send_device_ms_last") if out else None,
+        "h2d_bytes_per_step": 128,
+        "d2h_bytes_per_step": 128,
+        "stamp_errors": bad,
+        "what": "TensorBusClient.init_pair/register_tensors once, then per step: stamp H2D from pinned memory, "
+                "BatchHandler.transfer('send'|'recv') through command queue + agent + P2P kernels, stamp D2H and check",
+    }
 
 
 def main():

@@ -27,15 +27,11 @@ import threading
 import time
 import traceback
 import uuid
-from typing import Any, Generator
+from typing import Generator
 
 import torch
 import torch.distributed as dist
-from torch.distributed.tensor.placement_types import Partial
 
-from ..comm import chunk_to_bucket_ops, m2m_to_chunks
-from ..comm.bucket_exec import bucket_comm
-from ..comm.planner import plan_m2m
 from ..kvstore import KVStore, create_store
 from ..ops.hostlib import ExistentialError, Semaphore
 from .batch_state import BatchState

@@ -71,6 +71,14 @@ class BatchHandler:
         self.batch_id = batch_id
         self.pair_names = pair_names
         self._closed = False
+        self._pending = None  # completion of a non-blocking registration
+
+    def wait(self, timeout: float = 30.0) -> "BatchHandler":
+        """Wait for a registration started with `blocking=False`."""
+        if self._pending is not None:
+            self._pending.acquire(timeout)
+            self._pending = None
+        return self
 
     @property
     def client(self) -> "TensorBusClient":
@@ -214,8 +222,11 @@ class TensorBusClient:
         return None
 
     def register_tensors(self, batch_id: str, tensors: list[tuple[torch.Tensor, str]], bucket_size: int | None = None,
-                         timeout: float = 30.0) -> BatchHandler:
-        """Register `(tensor, pair_name)` entries as one batch; order within a pair pairs them with the remote side."""
+                         timeout: float = 30.0, blocking: bool = True) -> BatchHandler:
+        """Register `(tensor, pair_name)` entries as one batch; order within a pair pairs them with the remote side.
+
+        Blocks until every rank of both sides has registered (the reference always blocks).  A process that drives
+        several clients passes `blocking=False` to each and then calls `handler.wait(timeout)` on the handlers."""
         if not tensors:
             raise ValueError("tensors list cannot be empty")
         if any(t.is_cuda for t, _ in tensors) and self._peer is None:
@@ -225,8 +236,11 @@ class TensorBusClient:
         payload = [(pair, memoryview(encode_tensor(t, self._peer))) for t, pair in tensors]
         self._keepalive = getattr(self, "_keepalive", []) + [t for t, _ in tensors]
         msg = RegisterTensors(batch_id=batch_id, tensors=payload, bucket_size=bucket_size)
-        self._execute_command_with_semaphore(msg, "register_tensors", f"batch_{batch_id}", blocking=True, timeout=timeout)
-        return BatchHandler(self, batch_id, list(dict.fromkeys(pair for _, pair in tensors)))
+        done = self._execute_command_with_semaphore(msg, "register_tensors", f"batch_{batch_id}", blocking=blocking,
+                                                    timeout=timeout)
+        handler = BatchHandler(self, batch_id, list(dict.fromkeys(pair for _, pair in tensors)))
+        handler._pending = None if blocking else done
+        return handler
 
     def transfer(self, batch_id: str, transfer_type: Literal["send", "recv"], blocking: bool = False, timeout: float = 30.0):
         msg = Transfer(batch_id=batch_id, transfer_type=transfer_type)
