@@ -6,6 +6,7 @@ from .buckets import chunk_to_bucket_ops
 from .chunks import m2m_to_chunks
 from .ir import Bucket, Chunk, Endpoint, M2MMap, PartialFamily, Route, Transport
 from .planner import get_m2m_map, plan_m2m
+from .shaped import plan_for_shape, shaped_to_chunks
 
 __all__ = [
     "M2MMap",
@@ -21,4 +22,17 @@ __all__ = [
     "chunk_to_bucket_ops",
     "bucket_comm",
     "gather_broadcast_comm",
+    "plan_for_shape",
+    "shaped_to_chunks",
+    "P2PBatch",
+    "PairLayout",
 ]
+
+
+def __getattr__(name):
+    # the peer-to-peer executor loads the CUDA library; import it only when asked for
+    if name in ("P2PBatch", "PairLayout", "TransferTimeout", "link_local"):
+        from . import p2p
+
+        return getattr(p2p, name)
+    raise AttributeError(name)

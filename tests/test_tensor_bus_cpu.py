@@ -162,8 +162,14 @@ def _absent_peer_worker(rank, world, port, tag, tmp):
     try:
         if rank == 0:
             t0 = time.monotonic()
+            pending = client.init_pair("lonely", "trainer", "inference", 1, torch.tensor([0]), (Shard(0),), blocking=False)
+            worst = 0.0
+            while time.monotonic() - t0 < 0.8:  # the handshake is still waiting: the heartbeat must stay fresh
+                worst = max(worst, client.state.heartbeat_age())
+                time.sleep(0.05)
+            assert worst < 1.0
             with pytest.raises(TensorBusError, match="did not complete within"):
-                client.init_pair("lonely", "trainer", "inference", 1, torch.tensor([0]), (Shard(0),), timeout=20.0)
+                pending.acquire(20.0)
             assert 0.9 < time.monotonic() - t0 < 10.0
             assert client.state.matched("lonely") is None
             # the agent is still alive and answers the next command
