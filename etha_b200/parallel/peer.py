@@ -134,6 +134,22 @@ class PeerMemory:
             off += (sl.start or 0) * stride * dt.itemsize
         return SliceRef(base + off, desc.strides, dt, base, base + desc.region.size)
 
+    def as_tensor(self, desc: TensorDesc) -> torch.Tensor:
+        """A torch view of a described tensor in this process's address space (maps the region if needed).
+        Used when a library call needs a tensor object, e.g. the NCCL fallback across nodes."""
+        base = self.map_region(desc.region)
+        dt = desc.torch_dtype
+        span = 1 + sum((n - 1) * abs(st) for n, st in zip(desc.shape, desc.strides)) if all(desc.shape) else 0
+
+        class _Raw:
+            pass
+
+        raw = _Raw()
+        raw.__cuda_array_interface__ = {"shape": (max(span, 1) * dt.itemsize,), "typestr": "|u1",
+                                        "data": (base + desc.offset, False), "version": 2}
+        flat = torch.as_tensor(raw, device=self.device).view(dt)
+        return flat.as_strided(desc.shape, desc.strides)
+
     def close(self) -> None:
         for local in self._mapped.values():
             self._lib.etha_ipc_close(local)  # mappings adopted from elsewhere are unknown to it and left alone

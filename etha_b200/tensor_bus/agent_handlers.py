@@ -31,6 +31,12 @@ from .pair_state import PairState
 logger = logging.getLogger(__name__)
 
 
+def _hostname() -> str:
+    import socket
+
+    return socket.gethostname()
+
+
 def _wire_dtype(src: torch.dtype, dst: torch.dtype) -> torch.dtype:
     """Smaller item size wins; on a tie the SOURCE dtype travels and the consumer converts (the reference lets each
     side pick its own dtype on a tie and reinterprets bytes, src/etha/tensor_bus/agent.py:635-640)."""
@@ -142,6 +148,7 @@ class AgentHandlers:
             meta["descs"] = [obj for _, _, obj in entries]
             meta["flags"] = {d: self._peer.describe(t) for d, t in flags.items()}
             meta["gpu"] = str(torch.cuda.get_device_properties(self.device).uuid)
+            meta["host"] = _hostname()
         else:
             meta["descs"] = [(tuple(t.shape), str(t.dtype).replace("torch.", "")) for _, _, t in entries]
         self.store.set_bytes(f"batch:{batch_id}/rank:{self.rank}/meta", pickle.dumps(meta))
@@ -158,8 +165,15 @@ class AgentHandlers:
             if len(m["descs"]) != len(entries) or m["kind"] != kind:
                 raise ValueError(f"Batch {batch_id}: rank {r} registered {len(m['descs'])} {m['kind']} tensors, "
                                  f"rank {self.rank} registered {len(entries)} {kind} tensors")
-        if kind == "cuda":
+        if kind == "cuda" and len({m.get("host") for m in metas.values()}) == 1:
             self._build_p2p(batch, entries, metas, all_ranks, flags)
+        elif kind == "cuda":
+            # the pair spans machines: peer pointers end at the NVLink domain, so fall back to the bucket executor
+            # over NCCL on tensors rebuilt from the workers' descriptors
+            local = [(p, k, self._peer.as_tensor(d)) for p, k, d in entries]
+            for m in metas.values():
+                m["descs"] = [(tuple(d.shape), d.dtype) for d in m["descs"]]
+            self._build_buckets(batch, local, metas)
         else:
             self._build_buckets(batch, entries, metas)
         self.batches[batch_id] = batch
@@ -193,8 +207,8 @@ class AgentHandlers:
             batch.recv_buckets = chunk_to_bucket_ops(recv_chunks, size)
             # a direction is usable only if every pair of the batch has a plan for it (a Partial side can only send)
             pairs = [self.pairs[p] for p in batch.pair_names]
-            batch.send_exec = "gloo" if all(ps.m2m_send is not None for ps in pairs) else None
-            batch.recv_exec = "gloo" if all(ps.m2m_recv is not None for ps in pairs) else None
+            batch.send_exec = "bucket" if all(ps.m2m_send is not None for ps in pairs) else None
+            batch.recv_exec = "bucket" if all(ps.m2m_recv is not None for ps in pairs) else None
 
     def _chunks_for(self, m2m, smesh, splc, tmesh, tplc, source_shapes, target_shapes, source=None, target=None,
                     wire=None, k=0):
@@ -287,7 +301,7 @@ class AgentHandlers:
 
         ex = batch.send_exec if sending else batch.recv_exec
         t0 = time.perf_counter()
-        if ex == "gloo":
+        if ex == "bucket":
             bucket_comm(batch.send_buckets if sending else batch.recv_buckets)
         elif ex == "plain":
             yield from self._plain_transfer(batch, sending)
