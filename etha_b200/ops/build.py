@@ -32,16 +32,39 @@ NVCC_FLAGS = [
 ]
 
 
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared"]
+
+
 def _existing(names: list[str]) -> list[str]:
     return [os.path.join(CSRC, n) for n in names if os.path.exists(os.path.join(CSRC, n))]
 
 
-def _stale(target: str, sources: list[str]) -> bool:
-    if not os.path.exists(target):
+def _fingerprint(sources: list[str], flags: list[str]) -> str:
+    """Hash of everything that determines the binary: sources, headers and flags (file times do not survive copies)."""
+    import hashlib
+
+    h = hashlib.sha256(" ".join(flags).encode())
+    deps = sorted(sources + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".h")])
+    for path in deps:
+        h.update(os.path.basename(path).encode())
+        with open(path, "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def _stale(target: str, sources: list[str], flags: list[str]) -> bool:
+    stamp = target + ".stamp"
+    if not os.path.exists(target) or not os.path.exists(stamp):
         return True
-    t = os.path.getmtime(target)
-    deps = sources + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".h")]
-    return any(os.path.getmtime(s) > t for s in deps)
+    with open(stamp) as f:
+        return f.read().strip() != _fingerprint(sources, flags)
+
+
+def _write_stamp(target: str, sources: list[str], flags: list[str]) -> None:
+    tmp = target + f".stamp.tmp{os.getpid()}"
+    with open(tmp, "w") as f:
+        f.write(_fingerprint(sources, flags))
+    os.replace(tmp, target + ".stamp")
 
 
 def _run(cmd: list[str]) -> None:
@@ -59,7 +82,7 @@ def nvcc_path() -> str | None:
 
 def build_cuda_lib(force: bool = False, verbose: bool = False) -> str:
     sources = _existing(CUDA_SOURCES)
-    if not force and not _stale(CUDA_LIB, sources):
+    if not force and not _stale(CUDA_LIB, sources, NVCC_FLAGS):
         return CUDA_LIB
     nvcc = nvcc_path()
     if nvcc is None:
@@ -70,17 +93,19 @@ def build_cuda_lib(force: bool = False, verbose: bool = False) -> str:
         cmd.insert(1, "-Xptxas=-v")
     _run(cmd)
     os.replace(tmp, CUDA_LIB)
+    _write_stamp(CUDA_LIB, sources, NVCC_FLAGS)
     return CUDA_LIB
 
 
 def build_host_lib(force: bool = False) -> str:
     sources = _existing(HOST_SOURCES)
-    if not force and not _stale(HOST_LIB, sources):
+    if not force and not _stale(HOST_LIB, sources, HOST_FLAGS):
         return HOST_LIB
     cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
     tmp = HOST_LIB + f".tmp{os.getpid()}"
-    _run([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-o", tmp, *sources, "-lrt", "-lpthread"])
+    _run([cxx, *HOST_FLAGS, "-o", tmp, *sources, "-lrt", "-lpthread"])
     os.replace(tmp, HOST_LIB)
+    _write_stamp(HOST_LIB, sources, HOST_FLAGS)
     return HOST_LIB
 
 
