@@ -309,6 +309,9 @@ class AgentHandlers:
             yield from self._p2p_transfer(batch, ex, sending, epoch)
         ms = (time.perf_counter() - t0) * 1e3
         self.state.put(f"batch:{batch.batch_id}/state:last_{msg.transfer_type}_ms", f"{ms:.3f}".encode())
+        if epoch > 2:  # the rendezvous keys of older epochs are dead: every rank has passed them
+            for kind in ("go", "done"):
+                self.store.delete(f"batch:{batch.batch_id}/{kind}:{epoch - 2}/rank:{self.rank}")
         if not sending:
             batch.recv_done = epoch
             if self.rank == batch.local_leader:
