@@ -150,6 +150,10 @@ class P2PBatch:
                         producers_i_wait.add(primary)
                 if primary == self.rank:
                     mine.append((primary, s_index, cshape, dst_list))
+                elif reductions and self.rank in partial_family(smesh, reductions, primary).ranks:
+                    # the primary reads this rank's pending values over NVLink: this rank's memory is busy until the
+                    # primary's kernel has finished, so it waits for the primary's flag like a consumer does
+                    producers_i_wait.add(primary)
             # Producers walk their table in order, so if every producer served consumer 0 first, then consumer 1, ...
             # all of them would pour into the same GPU at the same time and share its ingress.  Rotate: producer
             # number p starts with consumer p, then p+1, ... (a permutation schedule over the NVSwitch).
@@ -167,6 +171,8 @@ class P2PBatch:
                     if qdesc is None or tuple(qdesc.shape) != tuple(sdesc.shape):
                         raise ValueError(f"Partial contributor {q} of tensor {i} has no matching shard")
                     srcs.append(self.peer.slice_ref(qdesc, s_index))
+                    if q != self.rank:
+                        consumers_i_write.add(q)  # tell the contributor when its shard has been read
                 dsts = []
                 for d_rank, d_index in dst_list:
                     ddesc = by_rank[d_rank]["dst"][i]

@@ -319,34 +319,33 @@ class AgentHandlers:
         logger.info("Agent %s: batch %s %s done in %.2f ms", self.rank, batch.batch_id, msg.transfer_type, ms)
 
     def _p2p_transfer(self, batch: BatchState, ex, sending: bool, epoch: int):
+        """Producers launch their copy table; every rank whose memory other ranks write (consumers) or read (Partial
+        contributors) then waits until those ranks are done — on the device with the bounded flag wait, or through
+        the KV store when another agent of the batch drives the same physical GPU."""
         shared_gpu = any(isinstance(k, dict) and k.get("shared_gpu") for k in batch.keepalive)
         stream = torch.cuda.current_stream(self.device)
         ex.epoch = epoch - 1
         ex.begin()
         done_prefix = f"batch:{batch.batch_id}/done:{epoch}"
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
         if sending:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
             ex.send(stream)
-            e1.record(stream)
-            while not e1.query():
-                yield
-            ex.check()
+        waits_on_device = bool(ex._producers) and not shared_gpu
+        if waits_on_device:
+            ex.recv(stream, timeout_s=min(self.store_timeout, 60.0))
+        e1.record(stream)
+        while not e1.query():
+            yield
+        ex.check()
+        if sending:
             self.state.put(f"batch:{batch.batch_id}/state:last_send_device_ms", f"{e0.elapsed_time(e1):.3f}".encode())
-            self.store.set(f"{done_prefix}/rank:{self.rank}", "1")
-        else:
+            self.store.set(f"{done_prefix}/rank:{self.rank}", "1")  # own copies are complete: published before any wait
+        if ex._producers and shared_gpu:
             producers = list(ex._producers)
-            if not shared_gpu:
-                ev = torch.cuda.Event()
-                ex.recv(stream, timeout_s=min(self.store_timeout, 60.0))
-                ev.record(stream)
-                while not ev.query():
-                    yield
-                ex.check()
-            else:
-                cands = [f"{done_prefix}/rank:{r}" for r in producers]
-                while len(self.store.poll_keys(f"{done_prefix}/rank:*", "1", cands)) < len(producers):
-                    yield
+            cands = [f"{done_prefix}/rank:{r}" for r in producers]
+            while len(self.store.poll_keys(f"{done_prefix}/rank:*", "1", cands)) < len(producers):
+                yield
 
     def _plain_transfer(self, batch: BatchState, sending: bool):
         """No layout was declared: tensor i goes whole to the same-index rank of the other side (reference
