@@ -147,6 +147,8 @@ def _mixed_dtype_worker(rank, world_size):
     case = ((2, 2), (S(0), S(1)), (4,), (S(0),), (16, 16), False)
     _run_case(rank, case, 1, False, dtype=torch.float32, wire_dtype=torch.bfloat16, tgt_dtype=torch.bfloat16)
     _run_case(rank, case, 1 << 20, False, dtype=torch.bfloat16, wire_dtype=torch.bfloat16, tgt_dtype=torch.float32)
+    # equal item sizes: the source dtype travels and the consumer converts values (never a byte reinterpretation)
+    _run_case(rank, case, 1, False, dtype=torch.float16, wire_dtype=torch.float16, tgt_dtype=torch.bfloat16)
 
 
 def test_mixed_dtypes():
