@@ -108,6 +108,20 @@ class KVStore(ABC):
                 raise TimeoutError(f"Timeout waiting for {expected_count} keys matching '{key_pattern}', got {len(found)}")
             time.sleep(self.poll_interval)
 
+    # ---- rendezvous of a known set of ranks (the agents' pre-transfer barrier) ---------------------------
+    def barrier_arrive(self, key_prefix: str, rank: int, *, component: str | None = None) -> None:
+        """Announce `rank` at the barrier named `key_prefix`. Backends with atomic counters override this."""
+        self.set(f"{key_prefix}/rank:{rank}", "1", component=component)
+
+    def barrier_count(self, key_prefix: str, ranks: list[int], *, component: str | None = None) -> int:
+        """How many of `ranks` have arrived (one poll, no waiting)."""
+        cands = [f"{key_prefix}/rank:{r}" for r in ranks]
+        return len(self.poll_keys(f"{key_prefix}/rank:*", "1", cands, component=component))
+
+    def barrier_forget(self, key_prefix: str, rank: int, *, component: str | None = None) -> None:
+        """Drop what `rank` left at a barrier every participant has passed."""
+        self.delete(f"{key_prefix}/rank:{rank}", component=component)
+
     def try_get(self, key: str, *, component: str | None = None) -> bytes | None:
         """`get` that treats an empty value (a deleted key on backends without delete) as missing."""
         v = self.get(key, component=component)

@@ -93,5 +93,15 @@ class TorchTCPStore(KVStore):
             )
         return super().wait_for_keys(key_pattern, expected_count, value, timeout, candidate_keys, component=component)
 
+    # TCPStore has an atomic counter: a barrier costs one round trip per poll instead of two per participant
+    def barrier_arrive(self, key_prefix: str, rank: int, *, component: str | None = None) -> None:  # noqa: ARG002
+        self._store.add(self._prefixed(f"{key_prefix}/count", component), 1)
+
+    def barrier_count(self, key_prefix: str, ranks: list[int], *, component: str | None = None) -> int:  # noqa: ARG002
+        return int(self._store.add(self._prefixed(f"{key_prefix}/count", component), 0))
+
+    def barrier_forget(self, key_prefix: str, rank: int, *, component: str | None = None) -> None:  # noqa: ARG002
+        return  # TCPStore cannot delete; one small counter per barrier is left behind
+
     def close(self, cleanup: bool = True) -> None:  # noqa: ARG002
         self._store = None

@@ -271,9 +271,9 @@ class AgentHandlers:
     # ---- Transfer -----------------------------------------------------------------------------------
     def _store_barrier(self, key_prefix: str, ranks):
         """All `ranks` set `{key_prefix}/rank:{r}`; yields until every key is there."""
-        self.store.set(f"{key_prefix}/rank:{self.rank}", "1")
-        cands = [f"{key_prefix}/rank:{r}" for r in ranks]
-        while len(self.store.poll_keys(f"{key_prefix}/rank:*", "1", cands)) < len(ranks):
+        ranks = list(ranks)
+        self.store.barrier_arrive(key_prefix, self.rank)
+        while self.store.barrier_count(key_prefix, ranks) < len(ranks):
             yield
 
     def _transfer_job(self, msg: Transfer):
@@ -310,8 +310,8 @@ class AgentHandlers:
         ms = (time.perf_counter() - t0) * 1e3
         self.state.put(f"batch:{batch.batch_id}/state:last_{msg.transfer_type}_ms", f"{ms:.3f}".encode())
         if epoch > 2:  # the rendezvous keys of older epochs are dead: every rank has passed them
-            for kind in ("go", "done"):
-                self.store.delete(f"batch:{batch.batch_id}/{kind}:{epoch - 2}/rank:{self.rank}")
+            self.store.barrier_forget(f"batch:{batch.batch_id}/go:{epoch - 2}", self.rank)
+            self.store.delete(f"batch:{batch.batch_id}/done:{epoch - 2}/rank:{self.rank}")
         if not sending:
             batch.recv_done = epoch
             if self.rank == batch.local_leader:

@@ -132,3 +132,15 @@ def test_create_store_factory(monkeypatch):
     e = create_store(gw.host, gw.port, backend="etcd", namespace="abc")
     assert isinstance(e, EtcdStore)
     gw.stop()
+
+
+def test_barrier_helpers(store):
+    ranks = [0, 1, 2]
+    assert store.barrier_count("b/go:1", ranks) == 0
+    store.barrier_arrive("b/go:1", 0)
+    store.barrier_arrive("b/go:1", 2)
+    assert store.barrier_count("b/go:1", ranks) == 2
+    store.barrier_arrive("b/go:1", 1)
+    assert store.barrier_count("b/go:1", ranks) == 3
+    assert store.barrier_count("b/go:2", ranks) == 0  # another barrier is independent
+    store.barrier_forget("b/go:1", 0)
