@@ -138,3 +138,115 @@ def test_tables_of_all_ranks_deliver_every_shard(case, overlap, monkeypatch):
         if b._signals is not None:
             want = sorted(by_rank[c]["flags"].region.base + by_rank[c]["flags"].offset + 4 * ranks.index(r) for c in b._consumers)
             assert sorted(b._signals.tolist()) == want
+
+
+# ---- typed ops: conversion and Partial collapse ---------------------------------------------------------------
+from torch.distributed.tensor.placement_types import Partial  # noqa: E402
+
+from etha_b200.comm.ir import PartialFamily, reduce_family_values  # noqa: E402
+from test_reshard_cpu import _make_source_local  # noqa: E402
+
+_CODE_DTYPE = {1: torch.float32, 2: torch.bfloat16, 3: torch.float16}
+_RED_NAMES = {0: "sum", 1: "avg", 2: "max", 3: "min", 4: "product"}
+
+
+def _emulate_typed(op: OpView, world: World):
+    """Conversion / reduction ops, one unit of `unit_elems` elements at a time, same order of operations as the kernels."""
+    sdt, ddt = _CODE_DTYPE[op.src_dtype], _CODE_DTYPE[op.dst_dtype]
+    n = op.unit_elems
+    fam = None
+    if op.mode == 2:
+        sizes = (op.red_size[0],) + ((op.red_size[1],) if op.red_size[1] > 1 else ())
+        ops = (_RED_NAMES[op.red_op[0]],) + ((_RED_NAMES[op.red_op[1]],) if op.red_size[1] > 1 else ())
+        fam = PartialFamily(ranks=tuple(range(op.nsrc)), sizes=sizes, ops=ops)
+    from test_table_emulation import _fast_div
+
+    for unit in range(op.total_units):
+        q = _fast_div(unit, op.div_mul[4], op.div_shr[4])
+        col = unit - q * op.inner_units
+        so, do = col * op.unit_bytes_src, col * op.unit_bytes_dst
+        for d in reversed(range(op.ndim)):
+            q2 = 0 if d == 0 else _fast_div(q, op.div_mul[d], op.div_shr[d])
+            i = q - q2 * op.extent[d]
+            so += i * op.src_stride[d]
+            do += i * op.dst_stride[d]
+            q = q2
+        vals = []
+        for k in range(op.nsrc):
+            _, buf, base = world.buffer_of(op.src[k])
+            a = op.src[k] - base + so
+            vals.append(torch.frombuffer(bytearray(buf[a : a + n * sdt.itemsize].tobytes()), dtype=sdt).clone())
+        out = reduce_family_values(vals, fam, sdt) if fam is not None else vals[0]
+        out_bytes = np.frombuffer(out.to(ddt).contiguous().view(torch.uint8).numpy().tobytes(), dtype=np.uint8)
+        for j in range(op.ndst):
+            _, dbuf, dbase = world.buffer_of(op.dst[j])
+            b = op.dst[j] - dbase + do
+            dbuf[b : b + n * ddt.itemsize] = out_bytes
+
+
+TYPED_CASES = [
+    ((4,), (Partial(),), (4,), (R,), (8, 16), torch.float32, torch.float32),
+    ((4,), (Partial("avg"),), (4,), (Shard(0),), (8, 16), torch.float32, torch.float32),
+    ((2, 2), (Shard(0), Partial()), (4,), (Shard(0),), (8, 16), torch.bfloat16, torch.bfloat16),
+    ((2, 2), (Partial(), Partial("max")), (2, 2), (R, Shard(1)), (8, 16), torch.float32, torch.bfloat16),
+    ((2, 3), (Partial(), Partial()), (2,), (R,), (8, 16), torch.float32, torch.float32),
+    ((2, 2), (Shard(0), Shard(1)), (4,), (Shard(0),), (16, 16), torch.float32, torch.bfloat16),
+    ((2,), (Partial(),), (2,), (Shard(0),), (5, 3), torch.float32, torch.float32),
+]
+
+
+@pytest.mark.parametrize("case", TYPED_CASES, ids=[str(i) for i in range(len(TYPED_CASES))])
+def test_typed_tables_convert_and_collapse(case, monkeypatch):
+    ss, sp, ts, tp, shape, sdt, tdt = case
+    ns, nt = math.prod(ss), math.prod(ts)
+    smesh, tmesh = torch.arange(ns).view(ss), torch.arange(ns, ns + nt).view(ts)
+    ranks = list(range(ns + nt))
+    eff = tuple(R if isinstance(p, Partial) else p for p in sp)
+    world = World(ranks)
+    logical, contribs = _make_source_local(0, smesh, sp, shape, sdt, False)
+    by_rank = {r: {"rank": r, "src": [None], "dst": [None]} for r in ranks}
+    targets = {}
+    for r in ranks:
+        if r < ns:
+            local = contribs[r] if contribs is not None else local_slice_of(logical, smesh, eff, r)
+            t, desc = world.alloc(r, local.shape, sdt)
+            t.copy_(local)
+            by_rank[r]["src"] = [desc]
+        else:
+            t, desc = world.alloc(r, local_slice_of(logical, tmesh, tp, r).shape, tdt)
+            by_rank[r]["dst"] = [desc]
+            targets[r] = t
+        _, by_rank[r]["flags"] = world.alloc(r, (len(ranks),), torch.int32)
+    monkeypatch.setattr(CopyTable, "finalize", lambda self, sm_count=None: self)
+    layout = PairLayout(smesh, sp, tmesh, tp)
+    batches = {}
+    for r in ranks:
+        b = P2PBatch.__new__(P2PBatch)
+        b.rank, b.ranks, b.device, b.peer = r, ranks, torch.device("cpu"), FakePeer(1000 + r)
+        b.nvls, b.tile_bytes, b.multicast_ops = None, 4096, 0
+        b._entries = [(layout, None, None)]
+        b._finish_build(by_rank)
+        batches[r] = b
+        for cls, tiles, raw in b.table._packed:
+            op = OpView.from_buffer_copy(raw)
+            if op.mode == 0:
+                for j in range(op.ndst):
+                    single = OpView.from_buffer_copy(raw)
+                    single.ndst, single.dst[0] = 1, op.dst[j]
+                    _, sbuf, sbase = world.buffer_of(op.src[0])
+                    _, dbuf, dbase = world.buffer_of(op.dst[j])
+                    _emulate(single, sbuf, dbuf, sbase, dbase)
+            else:
+                assert cls == 1
+                _emulate_typed(op, world)
+    for r, t in targets.items():
+        assert torch.equal(t, local_slice_of(logical, tmesh, tp, r).to(tdt)), f"rank {r}"
+    if any(isinstance(p, Partial) for p in sp):
+        # contributors wait for the primaries that read their shard; primaries signal them
+        red = [(i, p.reduce_op) for i, p in enumerate(sp) if isinstance(p, Partial)]
+        from etha_b200.comm.ir import partial_family
+
+        for r in range(ns):
+            readers = {p for p in range(ns) if p != r and batches[p].table._packed and r in partial_family(smesh, red, p).ranks}
+            assert readers <= set(batches[r]._producers)
+            assert all(r in batches[p]._consumers for p in readers)
