@@ -72,7 +72,6 @@ class _BucketState:
     data_recv: _Message | None = None
     wire: torch.Tensor | None = None
     wire_ready: bool = False
-    finished: bool = False
 
 
 class _Engine:

@@ -102,11 +102,6 @@ class PartialFamily:
     sizes: tuple[int, ...]
     ops: tuple[str, ...]
 
-    @property
-    def uniform_op(self) -> str | None:
-        """The single op when every level uses the same one (then the reduce is one flat pass)."""
-        return self.ops[0] if len(set(self.ops)) == 1 else None
-
 
 def partial_family(mesh: torch.Tensor, reductions: Sequence[tuple[int, str]], rank: int) -> PartialFamily | None:
     """Family of `rank` on `mesh` for the Partial mesh dims in `reductions` (None if no Partial)."""
@@ -203,7 +198,6 @@ class Chunk:
     contributes_to: int | None = None  # primary rank this reduce-only chunk feeds
     tensor_id: int = 0
     route_id: int = 0
-    buffer: torch.Tensor | None = None
 
     def __post_init__(self) -> None:
         if self.transfer_dtype is None:

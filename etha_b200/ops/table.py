@@ -129,8 +129,7 @@ class CopyTable:
                     if cls == 0 and not self._lib.etha_op_bulk_ok(buf):
                         self.bulk_ok = False
                     self._packed.append((cls, tiles, buf.raw))
-                mult = 1 if not multimem else 1
-                self.payload_bytes += numel * ddtype.itemsize * len(part) * mult
+                self.payload_bytes += numel * ddtype.itemsize * len(part)
         self.read_bytes += numel * src0.dtype.itemsize * len(srcs)
 
     def add_copy(self, src: torch.Tensor, dst: torch.Tensor) -> None:
