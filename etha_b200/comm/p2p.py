@@ -92,6 +92,7 @@ class P2PBatch:
         # with one multicast store instead of one store per replica
         self.nvls = nvls
         self.multicast_ops = 0
+        self.stripe_partial = True  # split the collapse of a Partial cell over the family members
         self._entries: list[tuple[PairLayout, torch.Tensor | None, torch.Tensor | None]] = []
         self.table: CopyTable | None = None
         self.epoch = 0
@@ -141,19 +142,15 @@ class P2PBatch:
         producers_i_wait: set[int] = set()
         self._all_local = True  # every destination lies in this process's memory on this device
         for i, (layout, src, dst) in enumerate(self._entries):
-            smesh = mesh_tensor_of(layout.source_mesh)
-            reductions, transfers = self._transfers_of(layout, i, by_rank)
+            items = self._work_items(layout, i, by_rank)
             mine = []
-            for primary, s_index, cshape, dst_list in transfers:
-                for d_rank, _ in dst_list:
-                    if d_rank == self.rank:
-                        producers_i_wait.add(primary)
-                if primary == self.rank:
-                    mine.append((primary, s_index, cshape, dst_list))
-                elif reductions and self.rank in partial_family(smesh, reductions, primary).ranks:
-                    # the primary reads this rank's pending values over NVLink: this rank's memory is busy until the
-                    # primary's kernel has finished, so it waits for the primary's flag like a consumer does
-                    producers_i_wait.add(primary)
+            for executor, members, s_index, cshape, dst_list, fam in items:
+                if executor == self.rank:
+                    mine.append((members, s_index, cshape, dst_list, fam))
+                # whoever writes into this rank's memory (itself included), or reads it as a Partial family member,
+                # must be waited for
+                if any(d_rank == self.rank for d_rank, _ in dst_list) or (executor != self.rank and self.rank in members):
+                    producers_i_wait.add(executor)
             # Producers walk their table in order, so if every producer served consumer 0 first, then consumer 1, ...
             # all of them would pour into the same GPU at the same time and share its ingress.  Rotate: producer
             # number p starts with consumer p, then p+1, ... (a permutation schedule over the NVSwitch).
@@ -161,16 +158,9 @@ class P2PBatch:
             if self.rank in s_ranks and len(t_ranks) > 1:
                 p, nt = s_ranks.index(self.rank), len(t_ranks)
                 mine.sort(key=lambda t: min((t_ranks.index(r) - p) % nt for r, _ in t[3]))
-            for primary, s_index, cshape, dst_list in mine:
-                sdesc = by_rank[primary]["src"][i]
-                fam = partial_family(smesh, reductions, primary) if reductions else None
-                members = fam.ranks if fam is not None else (primary,)
-                srcs = []
+            for members, s_index, cshape, dst_list, fam in mine:
+                srcs = [self.peer.slice_ref(by_rank[q]["src"][i], s_index) for q in members]
                 for q in members:
-                    qdesc = by_rank[q]["src"][i]
-                    if qdesc is None or tuple(qdesc.shape) != tuple(sdesc.shape):
-                        raise ValueError(f"Partial contributor {q} of tensor {i} has no matching shard")
-                    srcs.append(self.peer.slice_ref(qdesc, s_index))
                     if q != self.rank:
                         consumers_i_write.add(q)  # tell the contributor when its shard has been read
                 dsts = []
@@ -198,6 +188,47 @@ class P2PBatch:
             if self._producers else None
         )
         self._built = True
+
+    def _work_items(self, layout: "PairLayout", i: int, by_rank: dict[int, dict]):
+        """Every copy of tensor `i`, for all ranks: `(executing rank, source ranks, source slices, box shape,
+        [(consumer, slices)], family)`.
+
+        A plain route is executed by its producer.  A route of a Partial source is cut into one stripe per family
+        member along the first dimension that is long enough: member k collapses stripe k (reading the other members'
+        stripes over NVLink, its own locally, always in family order, so the result does not depend on who computes
+        it) and stores it into the consumers.  Every member then moves 1/F of the cell instead of the primary moving
+        all of it while the others idle."""
+        smesh = mesh_tensor_of(layout.source_mesh)
+        reductions, transfers = self._transfers_of(layout, i, by_rank)
+        items = []
+        for primary, s_index, cshape, dst_list in transfers:
+            if not reductions:
+                items.append((primary, (primary,), s_index, tuple(cshape), dst_list, None))
+                continue
+            fam = partial_family(smesh, reductions, primary)
+            sdesc = by_rank[primary]["src"][i]
+            for q in fam.ranks:
+                qdesc = by_rank[q]["src"][i]
+                if qdesc is None or tuple(qdesc.shape) != tuple(sdesc.shape):
+                    raise ValueError(f"Partial contributor {q} of tensor {i} has no matching shard")
+            n_members = len(fam.ranks)
+            dim = next((d for d, n in enumerate(cshape) if n >= n_members), None) if self.stripe_partial else None
+            if dim is None or n_members == 1:
+                items.append((primary, fam.ranks, s_index, tuple(cshape), dst_list, fam))
+                continue
+            extent = cshape[dim]
+            for k, member in enumerate(fam.ranks):
+                lo, hi = k * extent // n_members, (k + 1) * extent // n_members
+
+                def cut(index, lo=lo, hi=hi):
+                    index = list(index) + [slice(None)] * (len(cshape) - len(index))
+                    start = index[dim].start or 0
+                    index[dim] = slice(start + lo, start + hi)
+                    return tuple(index)
+
+                shape_k = tuple(hi - lo if d == dim else n for d, n in enumerate(cshape))
+                items.append((member, fam.ranks, cut(s_index), shape_k, [(r, cut(ix)) for r, ix in dst_list], fam))
+        return items
 
     def _transfers_of(self, layout: "PairLayout", i: int, by_rank: dict[int, dict]):
         """Normalised transfer list of tensor `i`: `(primary, source slices, box shape, [(consumer, slices), ...])`.

@@ -110,7 +110,7 @@ def test_tables_of_all_ranks_deliver_every_shard(case, overlap, monkeypatch):
     for r in ranks:
         b = P2PBatch.__new__(P2PBatch)
         b.rank, b.ranks, b.device, b.peer = r, ranks, torch.device("cpu"), FakePeer(1000 + r)
-        b.nvls, b.tile_bytes, b.multicast_ops = None, 4096, 0
+        b.nvls, b.tile_bytes, b.multicast_ops, b.stripe_partial = None, 4096, 0, True
         b._entries = [(layout, None, None)]
         b._finish_build(by_rank)
         batches[r] = b
@@ -223,7 +223,7 @@ def test_typed_tables_convert_and_collapse(case, monkeypatch):
     for r in ranks:
         b = P2PBatch.__new__(P2PBatch)
         b.rank, b.ranks, b.device, b.peer = r, ranks, torch.device("cpu"), FakePeer(1000 + r)
-        b.nvls, b.tile_bytes, b.multicast_ops = None, 4096, 0
+        b.nvls, b.tile_bytes, b.multicast_ops, b.stripe_partial = None, 4096, 0, True
         b._entries = [(layout, None, None)]
         b._finish_build(by_rank)
         batches[r] = b
@@ -246,6 +246,8 @@ def test_typed_tables_convert_and_collapse(case, monkeypatch):
         red = [(i, p.reduce_op) for i, p in enumerate(sp) if isinstance(p, Partial)]
         from etha_b200.comm.ir import partial_family
 
+        # the collapse is striped: every member of a family executes part of it
+        assert all(batches[r].table._packed for r in range(ns))
         for r in range(ns):
             readers = {p for p in range(ns) if p != r and batches[p].table._packed and r in partial_family(smesh, red, p).ranks}
             assert readers <= set(batches[r]._producers)
