@@ -34,6 +34,9 @@ def parse_args():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "qwen2-7b", "mixtral-8x7b", "qwen3-0.6b", "tiny"])
     p.add_argument("--bulk", type=int, default=-1, help="1: TMA bulk kernel for the fast class, 0: LD/ST kernel, -1: default")
+    p.add_argument("--engine", default="kernel", choices=["kernel", "dma-graph", "dma-streams"],
+                   help="kernel: every copy by the sm_100a kernels; dma-*: large remote bit copies by the DMA engines")
+    p.add_argument("--dma-min-kb", type=int, default=256)
     p.add_argument("--ctas-per-sm", type=int, default=2)
     p.add_argument("--tile-kb", type=int, default=64)
     p.add_argument("--bucket-mb", type=int, default=256, help="reference arm: bucket size in MiB (0 = one message per chunk)")
@@ -124,6 +127,8 @@ def run_ours(args) -> dict:
     ws = WeightSync(
         model, rank, list(range(world)), dev, smesh, tmesh, fsdp_layout(), vllm_tp_layout(), exchange=exchange,
         extra=[(stamp_layout, stamp_src, stamp_dst)], tile_bytes=args.tile_kb * 1024,
+        dma_min_bytes=args.dma_min_kb * 1024 if args.engine != "kernel" else None,
+        dma_mode="graph" if args.engine == "dma-graph" else "streams",
     ).build()
     # TMA bulk kernel by default when producer and consumer share the GPU (it only serves local destinations)
     bulk = bool(args.bulk) if args.bulk >= 0 else (world == 1)
@@ -143,6 +148,9 @@ def run_ours(args) -> dict:
     ws.check()
     bad = 0 if args.no_verify else ws.verify()
     bad = int(max_over_ranks(float(bad), world))
+    # every source value changes now (x 1/2, exact): the check after the timed loop can only pass if the timed
+    # transfers themselves delivered the data
+    ws.rescale_sources(0.5)
 
     # ---- device-timed region: K steps, events on the launching stream ---------------------------
     launches0 = table_mod.LAUNCH_COUNT[0] + ops.FLAG_LAUNCH_COUNT[0]
@@ -165,6 +173,8 @@ def run_ours(args) -> dict:
         t = torch.tensor([float(launches)], dtype=torch.float64)
         dist.all_reduce(t)
         launches = int(t.item())
+    bad_after = 0 if args.no_verify else ws.verify()
+    bad_after = int(max_over_ranks(float(bad_after), world))
     ms_total = max_over_ranks(e0.elapsed_time(e1), world)
     ms_step = ms_total / args.steps
     gbps = ws.payload_bytes / (ms_step * 1e-3) / 1e9
@@ -232,9 +242,14 @@ def run_ours(args) -> dict:
             "tensors": len(model.tensors),
             "payload_bytes": ws.payload_bytes,
             "l2_policy": "inputs larger than L2 (16 GB per sync vs 126 MB)",
-            "executor": "p2p copy table, " + ("TMA bulk kernel" if bulk else "LD/ST kernel"),
+            "executor": "p2p copy table, " + ("TMA bulk kernel" if bulk else "LD/ST kernel")
+                        + (f" + {ws.batch.table.n_dma_copies} DMA-engine copies ({args.engine})" if ws.batch.table.n_dma_copies else ""),
+            "dma_copies_per_step_this_rank": ws.batch.table.n_dma_copies,
             "verified_bit_exact": (bad == 0) if not args.no_verify else None,
             "mismatching_tensors": bad,
+            "verified_after_timed_region": (bad_after == 0) if not args.no_verify else None,
+            "verification": "bit-exact after warm-up; then every source is halved on the device and the targets are "
+                            "checked again after the timed loop against the halved values",
         },
         "e2e": {
             "value": round(e2e_gbps, 2),

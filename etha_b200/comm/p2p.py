@@ -80,6 +80,8 @@ class P2PBatch:
         tile_bytes: int = DEFAULT_TILE_BYTES,
         use_ipc: bool | None = None,
         nvls=None,
+        dma_min_bytes: int | None = None,
+        dma_mode: str = "graph",
     ):
         self.rank = rank
         self.ranks = list(ranks)
@@ -91,6 +93,9 @@ class P2PBatch:
         # optional `NvlsTeam`: routes whose consumers are exactly the team, at one common arena offset, are written
         # with one multicast store instead of one store per replica
         self.nvls = nvls
+        # copies of at least `dma_min_bytes` whose destination is on another GPU are run by the DMA engines (a CUDA
+        # graph of memcpy nodes built once, launched per transfer); None keeps every copy in the kernels
+        self.dma_min_bytes, self.dma_mode = dma_min_bytes, dma_mode
         self.multicast_ops = 0
         self.stripe_partial = True  # split the collapse of a Partial cell over the family members
         self._entries: list[tuple[PairLayout, torch.Tensor | None, torch.Tensor | None]] = []
@@ -118,10 +123,14 @@ class P2PBatch:
             "src": [self._describe(s) for _, s, _ in self._entries],
             "dst": [self._describe(t) for _, _, t in self._entries],
             "flags": self._describe(self._flags),
+            "gpu": self._gpu_id(),
         }
         everyone = self.exchange(mine)
         self._finish_build({e["rank"]: e for e in everyone})
         return self
+
+    def _gpu_id(self) -> str:
+        return str(torch.cuda.get_device_properties(self.device).uuid)
 
     def build_from(self, layouts: Sequence[PairLayout], by_rank: dict[int, dict], flags: torch.Tensor) -> "P2PBatch":
         """Build from descriptors gathered by the caller (the agent exchanges them through its KV store).
@@ -137,7 +146,9 @@ class P2PBatch:
         return self
 
     def _finish_build(self, by_rank: dict[int, dict]) -> None:
-        table = CopyTable(self.device, tile_bytes=self.tile_bytes)
+        table = CopyTable(self.device, tile_bytes=self.tile_bytes, dma_min_bytes=getattr(self, "dma_min_bytes", None),
+                          dma_mode=getattr(self, "dma_mode", "graph"))
+        my_gpu = by_rank[self.rank].get("gpu") if self.rank in by_rank else None
         consumers_i_write: set[int] = set()
         producers_i_wait: set[int] = set()
         self._all_local = True  # every destination lies in this process's memory on this device
@@ -164,14 +175,17 @@ class P2PBatch:
                     if q != self.rank:
                         consumers_i_write.add(q)  # tell the contributor when its shard has been read
                 dsts = []
+                all_remote = my_gpu is not None and len(members) == 1
                 for d_rank, d_index in dst_list:
                     ddesc = by_rank[d_rank]["dst"][i]
                     dsts.append(self.peer.slice_ref(ddesc, d_index))
                     if ddesc.region.pid != self.peer.pid or ddesc.region.device_index != self.device.index:
                         self._all_local = False
+                    if by_rank[d_rank].get("gpu") in (None, my_gpu):
+                        all_remote = False  # this GPU's own memory: the kernels copy HBM to HBM faster than the DMA engines
                     consumers_i_write.add(d_rank)
                 if not self._add_multicast(table, cshape, srcs, [r for r, _ in dst_list], by_rank, i, dsts, fam):
-                    table.add(cshape, srcs, dsts, fam.sizes if fam else (), fam.ops if fam else ())
+                    table.add(cshape, srcs, dsts, fam.sizes if fam else (), fam.ops if fam else (), dma_ok=all_remote)
         table.finalize()
         self.table = table
         # flags: slot k of a consumer's flag array belongs to producer ranks[k]
@@ -319,8 +333,9 @@ class P2PBatch:
             raise RuntimeError("build() first")
         if self._signals is None and self.table.empty:
             return
-        # the TMA kernel is used only when every destination is in this GPU's own memory
-        self.table.launch(stream, self._signals, self.epoch, ctas_per_sm=ctas_per_sm, bulk=bulk and self._all_local)
+        # `bulk`: run the 16-byte bit copies through the TMA ring kernel (local loads, plain bulk stores to local or
+        # peer memory) instead of the LD/ST kernel
+        self.table.launch(stream, self._signals, self.epoch, ctas_per_sm=ctas_per_sm, bulk=bulk)
 
     def recv(self, stream: torch.cuda.Stream | None = None, timeout_s: float = 10.0) -> None:
         """Enqueue the bounded wait for every producer that writes into this rank."""
@@ -358,6 +373,7 @@ def link_local(batches: Sequence[P2PBatch]) -> None:
         b._status = torch.zeros(2, dtype=torch.int32, device=b.device)
         gathered.append({
             "rank": b.rank,
+            "gpu": b._gpu_id(),
             "src": [b._describe(s) for _, s, _ in b._entries],
             "dst": [b._describe(t) for _, _, t in b._entries],
             "flags": b._describe(b._flags),

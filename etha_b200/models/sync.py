@@ -87,6 +87,8 @@ class WeightSync:
         tile_bytes: int | None = None,
         nvls: bool = False,
         nvls_tag: str = "ws",
+        dma_min_bytes: int | None = None,
+        dma_mode: str = "graph",
     ):
         self.model, self.rank, self.device, self.seed = model, rank, torch.device(device), seed
         self.smesh, self.tmesh = mesh_tensor_of(source_mesh), mesh_tensor_of(target_mesh)
@@ -146,11 +148,13 @@ class WeightSync:
                         t = self.rep_arena.tensor(offs[k], self.entries[k].spec.shape, target_dtype)
                         t.zero_()
                         self.entries[k].target = t
+        self.scale = 1.0  # every source currently holds `scale` x its seeded value (see `rescale_sources`)
         if fill and self.is_source:
             self.fill_sources(partial_scale)
 
         kw = {} if tile_bytes is None else {"tile_bytes": tile_bytes}
-        self.batch = P2PBatch(rank, ranks, self.device, exchange=exchange, peer=peer, nvls=self.team, **kw)
+        self.batch = P2PBatch(rank, ranks, self.device, exchange=exchange, peer=peer, nvls=self.team,
+                              dma_min_bytes=dma_min_bytes, dma_mode=dma_mode, **kw)
         for e in self.entries:
             self.batch.add(e.layout, e.source, e.target)
         for layout, s, t in extra:
@@ -186,13 +190,25 @@ class WeightSync:
             e.source.copy_(full[index].to(self.source_dtype))
             del full
 
+    def rescale_sources(self, factor: float = 0.5) -> None:
+        """Multiply every source shard by a power of two, in place on the device (exact in fp32/bf16/fp16 away from
+        the subnormals), and remember it: `verify()` then expects the rescaled values.  A benchmark calls this after
+        its warm-up, so that only transfers of the timed region can make the final `verify()` pass."""
+        m, _ = __import__("math").frexp(factor)
+        if m != 0.5:
+            raise ValueError("factor must be a power of two")
+        self.scale *= factor
+        if self.is_source:
+            for e in self.entries:
+                e.source.mul_(factor)
+
     def verify(self) -> int:
         """Bit-exact check of every target shard against the regenerated logical tensors. Returns mismatching tensors."""
         bad = 0
         if not self.is_target:
             return 0
         for k, e in enumerate(self.entries):
-            full = full_tensor_for(e.spec, k, self.seed, torch.float32, self.device)
+            full = full_tensor_for(e.spec, k, self.seed, torch.float32, self.device) * self.scale
             div = self._partial_divisor(e.layout.source_placements)
             if div > 1:
                 part = (full / div).to(self.source_dtype).to(torch.float32)

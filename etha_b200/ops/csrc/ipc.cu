@@ -87,6 +87,14 @@ int etha_ipc_close(uint64_t mapped_base) {
   return e == cudaSuccess ? 0 : fail(e, "cudaIpcCloseMemHandle");
 }
 
+// Copy-engine copy between two device addresses (either may be a mapped peer allocation): the DMA baseline the
+// copy kernels are compared with.
+int etha_copy_engine_d2d(uint64_t dst, uint64_t src, uint64_t bytes, void* stream) {
+  cudaError_t e = cudaMemcpyAsync(reinterpret_cast<void*>(dst), reinterpret_cast<const void*>(src), bytes,
+                                  cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+  return e == cudaSuccess ? 0 : fail(e, "cudaMemcpyAsync(device to device)");
+}
+
 int etha_enable_peer_access(int peer_device) {
   int cur = 0;
   cudaGetDevice(&cur);

@@ -101,18 +101,30 @@ int etha_wait_flags(const uint32_t* flags, const uint32_t* which, uint32_t n, ui
                     uint32_t* status, void* stream);
 int etha_set_flags(const uint64_t* signals, uint32_t n_signals, uint32_t epoch, void* stream);
 
-// TMA (cp.async.bulk) variant of the fast class for destinations in this GPU's own memory. Every op of the
-// table must satisfy etha_op_bulk_ok (16-byte bit copy, one source, one destination, at most one strided dim
-// whose rows are at least 512 bytes). One warp per CTA; `grid` is normally the SM count.
+// TMA (cp.async.bulk) variant of the fast class: bulk loads from this GPU's own memory into a shared-memory
+// ring, bulk stores (never multicast) to local or peer destinations. Every op of the table must satisfy
+// etha_op_bulk_ok (16-byte bit copy, one source, one or more plain destinations, at most one strided dim whose
+// rows are at least 512 bytes). One warp per CTA; `grid` is normally the SM count.
 int etha_op_bulk_ok(const struct M2NOp* op);
 int etha_m2n_bulk_launch(const struct M2NOp* ops, const uint32_t* tile_start, uint32_t n_ops, int grid,
                          uint32_t* sync_scratch, const uint64_t* signals, uint32_t n_signals, uint32_t epoch,
                          int do_signal, void* stream);
 
+// ---- copy-engine lowering (dma_graph.cu) -------------------------------------------------------
+// One DMA copy: `height` rows of `width` bytes, `spitch` / `dpitch` bytes between rows (height 1: one run).
+struct EthaDmaCopy {
+  uint64_t dst, src, width, height, dpitch, spitch;
+};
+int etha_op_dma_copies(const struct M2NOp* op, struct EthaDmaCopy* out);  // copies written (0: needs a kernel)
+int etha_dma_plan_create(const struct EthaDmaCopy* copies, uint32_t n, int use_graph, int n_streams, void** out);
+int etha_dma_plan_launch(void* plan, void* stream);
+int etha_dma_plan_destroy(void* plan);
+
 // ---- IPC / device helpers ---------------------------------------------------------------------
 int etha_ipc_export(uint64_t ptr, unsigned char* handle64, uint64_t* base, uint64_t* size);
 int etha_ipc_open(const unsigned char* handle64, uint64_t* mapped_base);
 int etha_ipc_close(uint64_t mapped_base);
+int etha_copy_engine_d2d(uint64_t dst, uint64_t src, uint64_t bytes, void* stream);
 int etha_enable_peer_access(int peer_device);
 int etha_device_info(int* sm_count, int* cc_major, int* cc_minor, int* multicast_supported);
 const char* etha_last_error(void);

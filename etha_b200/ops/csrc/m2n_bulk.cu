@@ -6,9 +6,12 @@
 // are written out with bulk stores from shared memory.  Loads run several stages ahead of the stores, so
 // well over 100 KiB per SM are in flight with almost no instruction issue.  No cluster, no multicast.
 //
-// Used for destinations in this GPU's own memory (the single-GPU / same-device path); peer destinations
-// keep the LD/ST kernel.  Every address and size handed to the copy engine is a multiple of 16 bytes: the
-// table packer admits only 16-byte units with 16-byte aligned bases and strides into this class.
+// Loads always read this GPU's own memory; the stores go to local memory, to a peer's memory over NVLink
+// (plain non-multicast bulk stores to the mapped peer address) or to several replicas one after the other
+// (a Replicate fan-out: the stage is read from HBM once and stored once per destination).  Every address
+// and size handed to the copy engine is a multiple of 16 bytes: the table packer admits only 16-byte units
+// with 16-byte aligned bases and strides into this class.  A side that is contiguous over the whole fill is
+// moved with ONE bulk copy per stage instead of one per matrix row.
 // Waits on the barriers are bounded: after the limit the CTA records an error word, drains its own stores
 // and returns.
 #include <cuda_runtime.h>
@@ -21,16 +24,25 @@
 
 namespace {
 
-constexpr int kStages = 6;
-constexpr uint32_t kStageBytes = 32 * 1024;
-constexpr int kMaxPieces = 64;  // pieces (row fragments) per stage
+#ifndef ETHA_BULK_STAGES
+#define ETHA_BULK_STAGES 6
+#endif
+#ifndef ETHA_BULK_STAGE_KB
+#define ETHA_BULK_STAGE_KB 32
+#endif
+constexpr int kStages = ETHA_BULK_STAGES;
+constexpr uint32_t kStageBytes = ETHA_BULK_STAGE_KB * 1024;
+constexpr uint32_t kMinRowBytes = 512;  // shortest matrix row the packer admits into this class
+// store pieces (row fragments) per stage: a fill that starts and ends inside a row touches one row more than
+// stage bytes / row bytes; the kernel still checks every fill against this bound before it issues anything
+constexpr int kMaxPieces = kStageBytes / kMinRowBytes + 2;
 
 struct StageMeta {
-  uint64_t dst[kMaxPieces];
+  int64_t dof[kMaxPieces];  // byte offset of the piece inside every destination slice
   uint32_t off[kMaxPieces];
   uint32_t bytes[kMaxPieces];
   uint32_t npieces;
-  uint32_t total;
+  uint32_t op;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -119,36 +131,55 @@ m2n_bulk_kernel(const M2NOp* __restrict__ ops, const uint32_t* __restrict__ tile
     }
   };
 
-  // issue the loads of one fill into stage s (all lanes), record the matching stores
-  auto issue_loads = [&](const FillPos& f, int s) {
+  // issue the loads of one fill into stage s (all lanes), record the matching stores; returns false (nothing
+  // issued, error word set) if the fill would need more store pieces than the stage's table holds
+  auto issue_loads = [&](const FillPos& f, int s) -> bool {
     const M2NOp& op = ops[f.op];
-    const uint32_t inner = op.ndim ? op.inner_units : 0xffffffffu;
-    const uint32_t r0 = op.ndim ? f.u0 / inner : 0;
-    const uint32_t r1 = op.ndim ? (f.u1 - 1) / inner : 0;
-    const uint32_t np = r1 - r0 + 1;
+    const bool rows = op.ndim != 0;
+    const uint32_t inner = rows ? op.inner_units : 0xffffffffu;
+    const uint32_t r0 = rows ? f.u0 / inner : 0;
+    const uint32_t r1 = rows ? (f.u1 - 1) / inner : 0;
+    const uint32_t nrows = r1 - r0 + 1;
+    const bool src_flat = !rows || op.src_stride[0] == (int64_t)inner * 16;
+    const bool dst_flat = !rows || op.dst_stride[0] == (int64_t)inner * 16;
+    const uint32_t n_store = dst_flat ? 1u : nrows;
+    if (n_store > (uint32_t)kMaxPieces) {
+      if (lane == 0) sync[1] = M2N_BAD_OP;
+      return false;
+    }
     StageMeta& m = meta[s];
+    unsigned char* buf = stage_buf + (size_t)s * kStageBytes;
     if (lane == 0) {
-      m.npieces = np;
-      m.total = (f.u1 - f.u0) * 16;
+      m.npieces = n_store;
+      m.op = f.op;
       mbar_expect_tx(&full[s], (f.u1 - f.u0) * 16);
     }
     __syncwarp();
-    for (uint32_t k = lane; k < np; k += 32) {
-      const uint32_t row = r0 + k;
-      const uint32_t a = op.ndim ? max(f.u0, row * inner) : f.u0;
-      const uint32_t b = op.ndim ? min(f.u1, (row + 1) * inner) : f.u1;
-      const uint32_t col = op.ndim ? a - row * inner : a;
-      const int64_t so = (int64_t)col * 16 + (op.ndim ? (int64_t)row * op.src_stride[0] : 0);
-      const int64_t dof = (int64_t)col * 16 + (op.ndim ? (int64_t)row * op.dst_stride[0] : 0);
-      const uint32_t off = (a - f.u0) * 16, bytes = (b - a) * 16;
-      if (k < kMaxPieces) {
-        m.dst[k] = op.dst[0] + dof;
-        m.off[k] = off;
-        m.bytes[k] = bytes;
+    if (dst_flat) {
+      if (lane == 0) { m.dof[0] = (int64_t)f.u0 * 16; m.off[0] = 0; m.bytes[0] = (f.u1 - f.u0) * 16; }
+    }
+    if (src_flat) {
+      if (lane == 0) bulk_load(buf, reinterpret_cast<const char*>(op.src[0]) + (int64_t)f.u0 * 16, (f.u1 - f.u0) * 16, &full[s]);
+    }
+    if (!(src_flat && dst_flat)) {
+      for (uint32_t k = lane; k < nrows; k += 32) {
+        const uint32_t row = r0 + k;
+        const uint32_t a = max(f.u0, row * inner);
+        const uint32_t b = min(f.u1, (row + 1) * inner);
+        const uint32_t col = a - row * inner;
+        const uint32_t off = (a - f.u0) * 16, bytes = (b - a) * 16;
+        if (!dst_flat) {
+          m.dof[k] = (int64_t)col * 16 + (int64_t)row * op.dst_stride[0];
+          m.off[k] = off;
+          m.bytes[k] = bytes;
+        }
+        if (!src_flat)
+          bulk_load(buf + off, reinterpret_cast<const char*>(op.src[0]) + (int64_t)col * 16 + (int64_t)row * op.src_stride[0],
+                    bytes, &full[s]);
       }
-      bulk_load(stage_buf + (size_t)s * kStageBytes + off, reinterpret_cast<const char*>(op.src[0]) + so, bytes, &full[s]);
     }
     __syncwarp();
+    return true;
   };
 
   FillPos pos;
@@ -157,7 +188,7 @@ m2n_bulk_kernel(const M2NOp* __restrict__ ops, const uint32_t* __restrict__ tile
   bool failed = false;
   // prologue: run kStages-1 fills ahead
   while (issued < kStages - 1 && (more = next_fill(pos))) {
-    issue_loads(pos, issued % kStages);
+    if (!issue_loads(pos, issued % kStages)) { more = false; break; }
     ++issued;
   }
   while (consumed < issued) {
@@ -173,16 +204,20 @@ m2n_bulk_kernel(const M2NOp* __restrict__ ops, const uint32_t* __restrict__ tile
     if (!ready) { failed = true; break; }
     const StageMeta& m = meta[s];
     const uint32_t np = m.npieces;
-    for (uint32_t k = lane; k < np; k += 32)
-      bulk_store(reinterpret_cast<void*>(m.dst[k]), stage_buf + (size_t)s * kStageBytes + m.off[k], m.bytes[k]);
+    const M2NOp& sop = ops[m.op];
+    const uint32_t nd = sop.ndst;
+    // piece k of destination j: the lanes walk the (destination, piece) pairs
+    for (uint32_t i = lane; i < np * nd; i += 32) {
+      const uint32_t j = i / np, k = i - j * np;
+      bulk_store(reinterpret_cast<char*>(sop.dst[j]) + m.dof[k], stage_buf + (size_t)s * kStageBytes + m.off[k], m.bytes[k]);
+    }
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     ++consumed;
     // the stage used one fill earlier may be refilled once its stores have read shared memory
     asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
     __syncwarp();
     if (more && (more = next_fill(pos))) {
-      issue_loads(pos, issued % kStages);
-      ++issued;
+      if (issue_loads(pos, issued % kStages)) ++issued; else more = false;
     }
   }
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");

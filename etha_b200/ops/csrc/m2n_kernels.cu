@@ -480,7 +480,10 @@ __device__ __forceinline__ void finish_and_signal(uint32_t* sync, const uint64_t
   }
 }
 
-constexpr int kUnroll = 4;
+#ifndef ETHA_FAST_UNROLL
+#define ETHA_FAST_UNROLL 4
+#endif
+constexpr int kUnroll = ETHA_FAST_UNROLL;
 
 // binary search of the op that owns `tile`, and (re)load of that op into shared memory
 __device__ __forceinline__ uint32_t locate_op(const M2NOp* __restrict__ ops, const uint32_t* __restrict__ tile_start,

@@ -50,8 +50,8 @@ int etha_op_class(const M2NOp* op) {
 }
 
 int etha_op_bulk_ok(const M2NOp* op) {
-  if (etha_op_class(op) != 0 || op->nsrc != 1 || op->ndst != 1 || (op->flags & M2N_FLAG_MULTIMEM)) return 0;
-  if (op->ndim == 1 && (uint64_t)op->inner_units * 16 < 512) return 0;
+  if (etha_op_class(op) != 0 || op->nsrc != 1 || op->ndst < 1 || (op->flags & M2N_FLAG_MULTIMEM)) return 0;
+  if (op->ndim == 1 && (uint64_t)op->inner_units * 16 < 512) return 0;  // kMinRowBytes of the TMA kernel
   return 1;
 }
 

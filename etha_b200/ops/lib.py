@@ -43,6 +43,10 @@ class OpSpec(C.Structure):
     ]
 
 
+class DmaCopy(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("dst", "src", "width", "height", "dpitch", "spitch")]
+
+
 _lock = threading.Lock()
 _lib = None
 
@@ -80,6 +84,16 @@ def cuda_lib() -> C.CDLL:
         lib.etha_ipc_open.restype = i32
         lib.etha_ipc_close.argtypes = [u64]
         lib.etha_ipc_close.restype = i32
+        lib.etha_copy_engine_d2d.argtypes = [u64, u64, u64, vp]
+        lib.etha_copy_engine_d2d.restype = i32
+        lib.etha_op_dma_copies.argtypes = [vp, C.POINTER(DmaCopy)]
+        lib.etha_op_dma_copies.restype = i32
+        lib.etha_dma_plan_create.argtypes = [C.POINTER(DmaCopy), u32, i32, i32, C.POINTER(vp)]
+        lib.etha_dma_plan_create.restype = i32
+        lib.etha_dma_plan_launch.argtypes = [vp, vp]
+        lib.etha_dma_plan_launch.restype = i32
+        lib.etha_dma_plan_destroy.argtypes = [vp]
+        lib.etha_dma_plan_destroy.restype = i32
         lib.etha_enable_peer_access.argtypes = [i32]
         lib.etha_enable_peer_access.restype = i32
         lib.etha_device_info.argtypes = [C.POINTER(i32)] * 4

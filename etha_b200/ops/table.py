@@ -27,6 +27,8 @@ DEFAULT_TILE_BYTES = 64 * 1024
 
 # kernels launched by CopyTable.launch in this process (benchmarks report it)
 LAUNCH_COUNT = [0]
+# copy-engine copies enqueued by CopyTable.launch in this process (not kernels; reported separately)
+DMA_COPY_COUNT = [0]
 
 
 def dtype_code(dt: torch.dtype) -> int:
@@ -51,19 +53,32 @@ class SliceRef:
 
 
 class CopyTable:
-    def __init__(self, device: torch.device | int | str, tile_bytes: int = DEFAULT_TILE_BYTES):
+    """`dma_min_bytes`: when set, a bit copy of at least that many bytes whose box is one run or the rows of a matrix,
+    and which the caller marks `dma_ok` (its destination is on another GPU), is not packed for the kernels but
+    becomes a memcpy node of a CUDA graph run by the DMA engines (`dma_mode="graph"`), or an asynchronous copy on
+    one of `dma_streams` side streams (`dma_mode="streams"`)."""
+
+    def __init__(self, device: torch.device | int | str, tile_bytes: int = DEFAULT_TILE_BYTES,
+                 dma_min_bytes: int | None = None, dma_mode: str = "graph", dma_streams: int = 8):
         self.device = torch.device(device) if not isinstance(device, torch.device) else device
         self.tile_bytes = int(tile_bytes)
+        self.dma_min_bytes = dma_min_bytes
+        self.dma_mode, self.dma_streams = dma_mode, dma_streams
+        self._dma: list[L.DmaCopy] = []
+        self._dma_plan = None
+        self.dma_bytes = 0
         self._lib = L.cuda_lib()
         self._op_size = self._lib.etha_sizeof_op()
-        self._packed: list[tuple[int, int, bytes]] = []  # (class, tiles, op bytes)
+        self._packed: list[tuple[int, int, bytes, bool]] = []  # (class, tiles, op bytes, TMA-capable)
         self.payload_bytes = 0  # bytes delivered (destination side, all replicas)
         self.read_bytes = 0
         self._final = False
         self._keepalive: list = []
         self.n_ops = [0, 0]
         self.n_tiles = [0, 0]
-        self.bulk_ok = True  # every fast-class op may go through the TMA kernel (local destinations only)
+        # fast-class ops are kept in two groups: those the TMA kernel can run (uploaded first) and the rest
+        self.n_bulk_ops = 0
+        self.n_bulk_tiles = 0
 
     # ---- building ---------------------------------------------------------------------------
     def add(
@@ -74,6 +89,7 @@ class CopyTable:
         reduce_sizes: Sequence[int] = (),
         reduce_ops: Sequence[str] = (),
         multimem: bool = False,
+        dma_ok: bool = False,
     ) -> None:
         """One op: `srcs` (1, or a Partial family in family order) -> every slice of `dsts`."""
         if self._final:
@@ -124,11 +140,20 @@ class CopyTable:
                 if rc != 0:
                     raise ValueError(f"cannot pack op ({rc}): {err.value.decode(errors='replace')}")
                 tiles = self._lib.etha_op_tiles(buf)
+                if tiles and dma_ok and self.dma_min_bytes is not None and numel * ddtype.itemsize >= self.dma_min_bytes:
+                    out = (L.DmaCopy * L.MAX_DST)()
+                    n = self._lib.etha_op_dma_copies(buf, out)
+                    if n > 0:
+                        for j in range(n):
+                            c = L.DmaCopy()
+                            C.memmove(C.byref(c), C.byref(out[j]), C.sizeof(L.DmaCopy))
+                            self._dma.append(c)
+                        self.dma_bytes += numel * ddtype.itemsize * n
+                        tiles = 0
                 if tiles:
                     cls = self._lib.etha_op_class(buf)
-                    if cls == 0 and not self._lib.etha_op_bulk_ok(buf):
-                        self.bulk_ok = False
-                    self._packed.append((cls, tiles, buf.raw))
+                    tma = cls == 0 and bool(self._lib.etha_op_bulk_ok(buf))
+                    self._packed.append((cls, tiles, buf.raw, tma))
                 self.payload_bytes += numel * ddtype.itemsize * len(part)
         self.read_bytes += numel * src0.dtype.itemsize * len(srcs)
 
@@ -152,27 +177,61 @@ class CopyTable:
         self.sm_count = sm_count
         self._ops_dev: list[torch.Tensor | None] = [None, None]
         self._tiles_dev: list[torch.Tensor | None] = [None, None]
+        self._tiles_rest_dev: torch.Tensor | None = None  # prefix sums of the fast ops the TMA kernel cannot run
+
+        def prefix(tiles):
+            starts = np.zeros(len(tiles) + 1, dtype=np.uint64)
+            np.cumsum(tiles, out=starts[1:])
+            if starts[-1] >= 2**32:
+                raise ValueError("too many tiles in one table")
+            return starts
+
+        def upload(starts):
+            return torch.from_numpy(starts.astype(np.uint32).view(np.int32).copy()).to(self.device)
+
         for cls in (0, 1):
-            members = [(t, raw) for c, t, raw in self._packed if c == cls]
+            members = [(t, raw, tma) for c, t, raw, tma in self._packed if c == cls]
+            if cls == 0:  # stable split: TMA-capable ops first, relative order kept inside both groups
+                members = [m for m in members if m[2]] + [m for m in members if not m[2]]
+                self.n_bulk_ops = sum(1 for m in members if m[2])
+                self.n_bulk_tiles = sum(m[0] for m in members if m[2])
             self.n_ops[cls] = len(members)
             if not members:
                 continue
-            starts = np.zeros(len(members) + 1, dtype=np.uint64)
-            np.cumsum([t for t, _ in members], out=starts[1:])
-            if starts[-1] >= 2**32:
-                raise ValueError("too many tiles in one table")
+            starts = prefix([t for t, _, _ in members])
             self.n_tiles[cls] = int(starts[-1])
-            blob = np.frombuffer(b"".join(raw for _, raw in members), dtype=np.uint8)
+            blob = np.frombuffer(b"".join(raw for _, raw, _ in members), dtype=np.uint8)
             self._ops_dev[cls] = torch.from_numpy(blob.copy()).to(self.device)
-            self._tiles_dev[cls] = torch.from_numpy(starts.astype(np.uint32).view(np.int32).copy()).to(self.device)
+            self._tiles_dev[cls] = upload(starts)
+            if cls == 0 and 0 < self.n_bulk_ops < len(members):
+                self._tiles_rest_dev = upload(prefix([t for t, _, _ in members[self.n_bulk_ops:]]))
         self._sync = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._packed = []
+        if self._dma:
+            arr = (L.DmaCopy * len(self._dma))(*self._dma)
+            plan = C.c_void_p()
+            with torch.cuda.device(self.device):
+                L.check(self._lib.etha_dma_plan_create(arr, len(self._dma), 1 if self.dma_mode == "graph" else 0,
+                                                       self.dma_streams, C.byref(plan)), "dma plan")
+            self._dma_plan = plan
         self._final = True
         return self
 
+    def __del__(self):
+        plan, self._dma_plan = getattr(self, "_dma_plan", None), None
+        if plan:
+            try:
+                self._lib.etha_dma_plan_destroy(plan)
+            except Exception:
+                pass
+
+    @property
+    def n_dma_copies(self) -> int:
+        return len(self._dma)
+
     @property
     def empty(self) -> bool:
-        return self.n_tiles[0] + self.n_tiles[1] == 0
+        return self.n_tiles[0] + self.n_tiles[1] == 0 and not self._dma
 
     # ---- launch -----------------------------------------------------------------------------
     def launch(
@@ -189,32 +248,50 @@ class CopyTable:
         s = (stream or torch.cuda.current_stream(self.device)).cuda_stream
         n_sig = 0 if signals is None else signals.numel()
         sig_ptr = 0 if signals is None else signals.data_ptr()
-        classes = [c for c in (0, 1) if self.n_tiles[c]]
-        if not classes:
+        # launches of this transfer: (kernel, ops, tile prefix sums, number of ops, tiles)
+        plan = []
+        if self.n_tiles[0]:
+            ops0, tiles0 = self._ops_dev[0].data_ptr(), self._tiles_dev[0].data_ptr()
+            if bulk and self.n_bulk_tiles:
+                plan.append(("bulk", ops0, tiles0, self.n_bulk_ops, self.n_bulk_tiles))
+                rest = self.n_ops[0] - self.n_bulk_ops
+                if rest:
+                    plan.append(("fast", ops0 + self.n_bulk_ops * self._op_size, self._tiles_rest_dev.data_ptr(), rest,
+                                 self.n_tiles[0] - self.n_bulk_tiles))
+            else:
+                plan.append(("fast", ops0, tiles0, self.n_ops[0], self.n_tiles[0]))
+        if self.n_tiles[1]:
+            plan.append(("general", self._ops_dev[1].data_ptr(), self._tiles_dev[1].data_ptr(), self.n_ops[1], self.n_tiles[1]))
+        dma = self._dma_plan is not None
+        if not plan or dma:
+            # with DMA copies in the transfer the kernels go first without a signal, then the copies, then the flags
+            for kernel, ops_ptr, tiles_ptr, n_ops, n_tiles in plan:
+                self._launch_kernel(kernel, ops_ptr, tiles_ptr, n_ops, n_tiles, ctas_per_sm, (sig_ptr, 0, 0, 0), s)
+            if dma:
+                L.check(self._lib.etha_dma_plan_launch(self._dma_plan, s), "dma launch")
+                DMA_COPY_COUNT[0] += len(self._dma)
             if n_sig:
                 L.check(self._lib.etha_set_flags(sig_ptr, n_sig, epoch & 0xFFFFFFFF, s), "set_flags")
                 LAUNCH_COUNT[0] += 1
             return
-        for c in classes:
-            last = c == classes[-1]
+        for i, (kernel, ops_ptr, tiles_ptr, n_ops, n_tiles) in enumerate(plan):
+            last = i == len(plan) - 1
+            sig = (sig_ptr, n_sig, epoch & 0xFFFFFFFF, 1) if (last and n_sig) else (sig_ptr, 0, epoch & 0xFFFFFFFF, 0)
+            self._launch_kernel(kernel, ops_ptr, tiles_ptr, n_ops, n_tiles, ctas_per_sm, sig, s)
+
+    def _launch_kernel(self, kernel, ops_ptr, tiles_ptr, n_ops, n_tiles, ctas_per_sm, sig, s) -> None:
+        if kernel == "bulk":
+            rc = self._lib.etha_m2n_bulk_launch(ops_ptr, tiles_ptr, n_ops, min(n_tiles, self.sm_count),
+                                                self._sync.data_ptr(), *sig, s)
+        else:
+            general = kernel == "general"
             # the fast kernel is compiled for two 512-thread CTAs per SM; the general one reports its own occupancy
-            per_sm = ctas_per_sm if c == 0 else max(ctas_per_sm, self._lib.etha_general_ctas_per_sm())
-            grid = min(self.n_tiles[c], self.sm_count * per_sm)
-            if bulk and c == 0 and self.bulk_ok:
-                rc = self._lib.etha_m2n_bulk_launch(
-                    self._ops_dev[c].data_ptr(), self._tiles_dev[c].data_ptr(), self.n_ops[c],
-                    min(self.n_tiles[c], self.sm_count), self._sync.data_ptr(), sig_ptr, n_sig if last else 0,
-                    epoch & 0xFFFFFFFF, 1 if (last and n_sig) else 0, s,
-                )
-            else:
-                rc = self._lib.etha_m2n_launch(
-                    self._ops_dev[c].data_ptr(), self._tiles_dev[c].data_ptr(), self.n_ops[c], c, grid, 0,
-                    self._sync.data_ptr(), sig_ptr, n_sig if last else 0, epoch & 0xFFFFFFFF,
-                    1 if (last and n_sig) else 0, s,
-                )
-            L.check(rc, "m2n launch")
-            LAUNCH_COUNT[0] += 1
+            per_sm = max(ctas_per_sm, self._lib.etha_general_ctas_per_sm()) if general else ctas_per_sm
+            rc = self._lib.etha_m2n_launch(ops_ptr, tiles_ptr, n_ops, int(general), min(n_tiles, self.sm_count * per_sm), 0,
+                                           self._sync.data_ptr(), *sig, s)
+        L.check(rc, "m2n launch")
+        LAUNCH_COUNT[0] += 1
 
     def error_word(self) -> int:
         """Device-side error word of the last launches (synchronizes)."""
-        return int(self._sync[1].item())
+        return int(self._sync[1].item()) if (self.n_tiles[0] + self.n_tiles[1]) else 0

@@ -257,6 +257,7 @@ class AgentHandlers:
                     "src": descs if r in src_side else [None] * len(descs),
                     "dst": descs if r not in src_side else [None] * len(descs),
                     "flags": metas[r]["flags"][direction],
+                    "gpu": metas[r].get("gpu"),
                 }
             b = P2PBatch(self.rank, all_ranks, self.device, peer=self._peer, use_ipc=True)
             return b.build_from(layouts, by_rank, flags[direction])

@@ -180,7 +180,7 @@ def test_tma_bulk_kernel_matches_ldst(shape, cols):
     t = CopyTable(DEV)
     t.add_copy(sv, dst)
     t.finalize()
-    assert t.bulk_ok
+    assert t.n_bulk_ops == t.n_ops[0] == 1
     for epoch in (1, 2):
         dst.zero_()
         t.launch(signals=addrs, epoch=epoch, bulk=True)
@@ -198,13 +198,38 @@ def test_tma_bulk_many_ops_and_fallback():
     t.finalize()
     t.launch(bulk=True)
     torch.cuda.synchronize()
-    assert t.bulk_ok and all(torch.equal(s, d) for s, d in zip(srcs, dsts))
-    # a fan-out op is not eligible: the table quietly uses the LD/ST kernel
+    assert t.n_bulk_ops == 9 and all(torch.equal(s, d) for s, d in zip(srcs, dsts))
+    # a fan-out is read once per stage and stored to every replica by the TMA kernel
     a, b1, b2 = _rand((256, 256), torch.float32, 40), torch.zeros(256, 256, device=DEV), torch.zeros(256, 256, device=DEV)
     t2 = CopyTable(DEV)
     t2.add((256, 256), [SliceRef.of(a)], [SliceRef.of(b1), SliceRef.of(b2)])
     t2.finalize()
-    assert not t2.bulk_ok
+    assert t2.n_bulk_ops == 1
     t2.launch(bulk=True)
     torch.cuda.synchronize()
-    assert torch.equal(a, b1) and torch.equal(a, b2)
+    assert t2.error_word() == 0 and torch.equal(a, b1) and torch.equal(a, b2)
+
+
+def test_tma_bulk_mixed_table_splits_per_op():
+    """Rows shorter than 512 bytes stay with the LD/ST kernel, everything else of the fast class goes through the
+    TMA ring; the flag is published by whichever kernel runs last."""
+    wide = _rand((1024, 4096), torch.bfloat16, 50)          # strided source rows of 2 KiB -> contiguous destination
+    narrow = _rand((4096, 512), torch.bfloat16, 51)         # 128-byte rows: not TMA-capable
+    vec = _rand((1024,), torch.bfloat16, 52)                # one 2 KiB run, three replicas
+    d_wide = torch.zeros(1024, 1024, dtype=torch.bfloat16, device=DEV)
+    d_narrow = torch.zeros(4096, 512, dtype=torch.bfloat16, device=DEV)
+    reps = [torch.zeros(1024, dtype=torch.bfloat16, device=DEV) for _ in range(3)]
+    flags = torch.zeros(1, dtype=torch.int32, device=DEV)
+    addrs = torch.tensor([flags.data_ptr()], dtype=torch.int64, device=DEV)
+    t = CopyTable(DEV)
+    t.add_copy(narrow[:, 64:128], d_narrow[:, 64:128])
+    t.add_copy(wide[:, 1024:2048], d_wide)
+    t.add((1024,), [SliceRef.of(vec)], [SliceRef.of(r) for r in reps])
+    t.finalize()
+    assert t.n_ops[0] == 3 and t.n_bulk_ops == 2
+    t.launch(signals=addrs, epoch=7, bulk=True)
+    torch.cuda.synchronize()
+    assert t.error_word() == 0 and flags.tolist() == [7]
+    assert torch.equal(d_wide, wide[:, 1024:2048])
+    assert all(torch.equal(r, vec) for r in reps)
+    assert torch.equal(d_narrow[:, 64:128], narrow[:, 64:128]) and int(d_narrow[:, :64].count_nonzero()) == 0
