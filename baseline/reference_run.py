@@ -73,7 +73,7 @@ def run(args, ref_dir: str) -> dict:
         sys.path.insert(0, root)
     _install_stubs()
     sys.path.insert(0, ref_dir)
-    from bench import max_over_ranks, meshes_for, model_of  # shared harness pieces only
+    from bench import layout_for, max_over_ranks, model_of  # shared harness pieces only
 
     # initialise exactly as the reference's agent does (src/etha/tensor_bus/agent.py:103-107): no eager
     # communicator, so every peer pair gets its own lazily created NCCL communicator and stream
@@ -93,21 +93,27 @@ def run(args, ref_dir: str) -> dict:
         return {}
     from torch.distributed.device_mesh import DeviceMesh
 
-    from etha_b200.models import fsdp_layout, vllm_tp_layout
     from etha_b200.models.sync import full_tensor_for, local_shape_and_offset
     from etha_b200.utils.clocks import ClockSampler
-    from torch.distributed.tensor.placement_types import Replicate
+    from torch.distributed.tensor.placement_types import Partial, Replicate
 
     dev = torch.device("cuda", torch.cuda.current_device())
     model = model_of(args.model)
-    smesh_t, tmesh_t, par = meshes_for(world)
-    s_rule, t_rule = fsdp_layout(), vllm_tp_layout()
-    is_src, is_dst = rank in smesh_t.tolist(), rank in tmesh_t.tolist()
+    smesh_t, tmesh_t, s_rule, t_rule, par, _ = layout_for(args, world)
+    is_src, is_dst = rank in smesh_t.reshape(-1).tolist(), rank in tmesh_t.reshape(-1).tolist()
     dtype = torch.bfloat16
     seed = 2
 
+    def partial_div(plc):
+        n = 1
+        for size, p in zip(smesh_t.shape, plc):
+            if isinstance(p, Partial):
+                n *= size
+        return n
+
     def shard(spec, k, mesh_t, plc):
-        full = full_tensor_for(spec, k, seed, torch.float32, dev)
+        # a Partial("sum") source holds value / group size on every contributor (exact for powers of two)
+        full = full_tensor_for(spec, k, seed, torch.float32, dev) / partial_div(plc)
         shape, off = local_shape_and_offset(spec.shape, mesh_t, plc, rank)
         out = full[tuple(slice(o, o + n) for o, n in zip(off, shape))].to(dtype).contiguous()
         del full
@@ -115,22 +121,39 @@ def run(args, ref_dir: str) -> dict:
 
     chunks = []
     targets = []
+    sources = []
     payload = 0
     if world > 1:
         smesh = DeviceMesh("cpu", smesh_t)
         tmesh = DeviceMesh("cpu", tmesh_t)
         maps = {}
+        groups = {}
+        source_ranks = smesh_t.reshape(-1).tolist()
         for k, spec in enumerate(model.tensors):
             sp, tp = tuple(s_rule(spec)), tuple(t_rule(spec))
             if (sp, tp) not in maps:
                 maps[(sp, tp)] = get_m2m_map(smesh, sp, tmesh, tp, group=dist.group.WORLD, device="cpu")
+                groups[(sp, tp)] = None
+                if maps[(sp, tp)].source_partial_reductions:
+                    # the reference's own Partial path: one NCCL sub-group per Partial mesh dim, created by every rank in
+                    # the same order, and an all-reduce per chunk inside Chunk.prepare (src/etha/tensor_bus/agent.py:
+                    # 46-70, 391-403; src/etha/comm/ir.py:101-126)
+                    from etha.pg_utils import get_or_create_process_group
+                    from etha.tensor_bus.agent import _create_partial_groups
+
+                    full_group = get_or_create_process_group(source_ranks)
+                    groups[(sp, tp)] = _create_partial_groups(smesh_t, maps[(sp, tp)].source_partial_reductions, rank,
+                                                              source_ranks, full_group)
             src = shard(spec, k, smesh_t, sp) if is_src else None
+            if src is not None:
+                sources.append(src)
             tgt = None
             if is_dst:
                 shape, _ = local_shape_and_offset(spec.shape, tmesh_t, tp, rank)
                 tgt = torch.zeros(shape, dtype=dtype, device=dev)
-                targets.append((k, spec, tp, tgt))
-            chunks += m2m_to_chunks(maps[(sp, tp)], rank=rank, source_tensor=src, target_tensor=tgt)
+                targets.append((k, spec, sp, tp, tgt))
+            chunks += m2m_to_chunks(maps[(sp, tp)], rank=rank, source_tensor=src, target_tensor=tgt,
+                                    source_partial_groups=groups[(sp, tp)] if is_src else None)
             copies = 1
             for size, p in zip(tmesh_t.shape, tp):
                 if isinstance(p, Replicate):
@@ -152,11 +175,26 @@ def run(args, ref_dir: str) -> dict:
                 src_slice=(slice(0, 1),) + (slice(None),) * nd, dst_slice=(slice(1, 2),) + (slice(None),) * nd,
                 tensor=both,
             ))
-            targets.append((k, spec, tuple(t_rule(spec)), both[1]))
+            targets.append((k, spec, tuple(s_rule(spec)), tuple(t_rule(spec)), both[1]))
+            sources.append(both[0])
             n = dtype.itemsize
             for s in spec.shape:
                 n *= s
             payload += n
+
+    scale = [1.0]
+
+    def mismatches() -> int:
+        n_bad = 0
+        for k, spec, sp, tp, tgt in targets:
+            div = partial_div(sp)
+            full = full_tensor_for(spec, k, seed, torch.float32, dev) * scale[0]
+            full = ((full / div).to(dtype).to(torch.float32) * div).to(dtype) if div > 1 else full.to(dtype)
+            shape, off = local_shape_and_offset(spec.shape, tmesh_t, tp, rank)
+            if not torch.equal(tgt, full[tuple(slice(o, o + n) for o, n in zip(off, shape))]):
+                n_bad += 1
+            del full
+        return n_bad
 
     modes = {"chunk": 1}
     if args.bucket_mb > 0:
@@ -164,18 +202,19 @@ def run(args, ref_dir: str) -> dict:
     results = {}
     clocks = {}
     bad = 0
+    bad_after = 0
     for name, bucket_size in modes.items():
         buckets = chunk_to_bucket_ops(chunks=chunks, bucket_size=bucket_size)
         for _ in range(args.warmup):
             bucket_comm(buckets=buckets)
         torch.cuda.synchronize()
         if not args.no_verify and not results:
-            for k, spec, tp, tgt in targets:
-                full = full_tensor_for(spec, k, seed, torch.float32, dev).to(dtype)
-                shape, off = local_shape_and_offset(spec.shape, tmesh_t, tp, rank)
-                if not torch.equal(tgt, full[tuple(slice(o, o + n) for o, n in zip(off, shape))]):
-                    bad += 1
-                del full
+            bad += mismatches()
+        # every source value is halved (exact) between warm-up and the timed loop, as in the other arm: the check
+        # after the loop can only pass if the timed transfers delivered the data
+        for t in sources:
+            t.mul_(0.5)
+        scale[0] *= 0.5
         sampler = ClockSampler(dev.index).start()
         torch.cuda.synchronize()
         dist.barrier()
@@ -187,7 +226,10 @@ def run(args, ref_dir: str) -> dict:
         torch.cuda.synchronize()
         clocks[name] = sampler.stop()
         results[name] = max_over_ranks(e0.elapsed_time(e1), world) / args.steps
+        if not args.no_verify:
+            bad_after += mismatches()
         dist.barrier()
+    bad_after = int(max_over_ranks(float(bad_after), world))
     bad = int(max_over_ranks(float(bad), world))
     best = min(results, key=results.get)
     ms = results[best]
@@ -208,6 +250,7 @@ def run(args, ref_dir: str) -> dict:
         "config": {
             "model": args.model,
             "parallelism": par,
+            "layout": args.layout,
             "tensors": len(model.tensors),
             "payload_bytes": payload,
             "executor": "reference etha.comm.bucket_comm over NCCL" if world > 1 else "reference LOCAL chunks (hand-built), bucket_comm",
@@ -215,6 +258,7 @@ def run(args, ref_dir: str) -> dict:
             "ms_per_step_by_mode": {k: round(v, 4) for k, v in results.items()},
             "l2_policy": "inputs larger than L2",
             "verified_bit_exact": bad == 0 if not args.no_verify else None,
+            "verified_after_timed_region": bad_after == 0 if not args.no_verify else None,
         },
         "e2e": {"value": round(payload / (ms * 1e-3) / 1e9, 2), "unit": "GB/s",
                 "what": "bucket_comm is the reference's public call and ends with a device synchronize; no separate end-to-end path",

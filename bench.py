@@ -33,10 +33,18 @@ def parse_args():
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "qwen2-7b", "mixtral-8x7b", "qwen3-0.6b", "tiny"])
+    p.add_argument("--layout", default="fsdp-tp", choices=["fsdp-tp", "partial2x2-tp"],
+                   help="fsdp-tp: Shard(0) over N/2 producers (stacked experts: expert parallel) -> TP over N/2 consumers; "
+                        "partial2x2-tp: source mesh (2, N/4) with (Partial, Shard(0)) -> N/2 consumers, norms and "
+                        "embeddings Replicate, linears TP (needs N >= 4)")
+    p.add_argument("--nvls", type=int, default=0, help="1: Replicate targets live in a multicast-bound arena (multimem.st fan-out)")
+    p.add_argument("--source-dtype", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--bulk", type=int, default=-1, help="1: TMA bulk kernel for the fast class, 0: LD/ST kernel, -1: default")
-    p.add_argument("--engine", default="kernel", choices=["kernel", "dma-graph", "dma-streams"],
-                   help="kernel: every copy by the sm_100a kernels; dma-*: large remote bit copies by the DMA engines")
-    p.add_argument("--dma-min-kb", type=int, default=256)
+    p.add_argument("--engine", default="auto", choices=["auto", "kernel", "dma-graph", "dma-streams"],
+                   help="kernel: every copy by the sm_100a kernels; dma-*: the largest remote bit copies run on the DMA "
+                        "engines next to the kernels; auto: dma-graph across GPUs, kernel on one GPU")
+    p.add_argument("--dma-min-kb", type=int, default=1024)
+    p.add_argument("--dma-fraction", type=float, default=0.7, help="share of the delivered bytes given to the DMA engines")
     p.add_argument("--ctas-per-sm", type=int, default=2)
     p.add_argument("--tile-kb", type=int, default=64)
     p.add_argument("--bucket-mb", type=int, default=256, help="reference arm: bucket size in MiB (0 = one message per chunk)")
@@ -93,13 +101,44 @@ def meshes_for(n: int):
     return torch.arange(half), torch.arange(half, n), f"fsdp{half}->tp{half}"
 
 
+def layout_for(args, n: int):
+    """(source mesh, target mesh, source rule, target rule, description, bytes the busiest GPU sends or receives)
+    of the benchmark's layout; shared by both arms so that they run the same configuration."""
+    import torch
+    from torch.distributed.tensor.placement_types import Partial, Replicate, Shard
+
+    from etha_b200.models import fsdp_layout, vllm_tp_layout
+
+    model = model_of(args.model)
+    if args.layout == "fsdp-tp":
+        smesh, tmesh, par = meshes_for(n)
+        if "mixtral" in args.model:
+            par = par.replace("fsdp", "ep+fsdp")
+        k = max(n // 2, 1)
+        return smesh, tmesh, fsdp_layout(), vllm_tp_layout(), par, model.numel * 2 / k
+    if n < 4 or n % 4:
+        raise SystemExit("layout partial2x2-tp needs 4 or 8 GPUs (a 2 x N/4 producer mesh and N/2 consumers)")
+    half = n // 2
+    smesh, tmesh = torch.arange(half).view(2, half // 2), torch.arange(half, n)
+    tp_rule = vllm_tp_layout()
+
+    def t_rule(t):
+        return (Replicate(),) if t.kind in ("norm", "vocab", "router") else tp_rule(t)
+
+    rep = sum(2 * torch.Size(t.shape).numel() for t in model.tensors if t.kind in ("norm", "vocab", "router"))
+    # every consumer receives its 1/(N/2) of the TP tensors and all of the Replicate ones; the 2 x N/4 producers send
+    # the same amount in total, so a consumer's ingress is the bound
+    busiest = (model.numel * 2 - rep) / half + rep
+    return (smesh, tmesh, lambda t: (Partial(), Shard(0)), t_rule,
+            f"(Partial, Shard(0)) on 2x{half // 2} -> tp{half} (norms, embeddings Replicate)", busiest)
+
+
 def run_ours(args) -> dict:
     import torch
     import torch.distributed as dist
 
     from etha_b200 import ops
     from etha_b200.comm.p2p import PairLayout
-    from etha_b200.models import fsdp_layout, vllm_tp_layout
     from etha_b200.models.sync import WeightSync
     from etha_b200.ops import table as table_mod
     from etha_b200.utils.clocks import ClockSampler
@@ -108,7 +147,9 @@ def run_ours(args) -> dict:
     rank, world, group = init_dist(args.gpus)
     dev = torch.device("cuda", torch.cuda.current_device())
     model = model_of(args.model)
-    smesh, tmesh, par = meshes_for(world)
+    smesh, tmesh, s_rule, t_rule, par, busiest_bytes = layout_for(args, world)
+    if args.engine == "auto":
+        args.engine = "dma-graph" if world > 1 else "kernel"
 
     def exchange(obj):
         if world == 1:
@@ -119,16 +160,18 @@ def run_ours(args) -> dict:
 
     # a version stamp travels with the weights: the producer uploads it from pinned host memory each
     # step, every consumer reads it back after the sync (this is the end-to-end check of a step)
-    is_src = rank in smesh.tolist()
-    is_dst = rank in tmesh.tolist()
+    is_src = rank in smesh.reshape(-1).tolist()
+    is_dst = rank in tmesh.reshape(-1).tolist()
     stamp_src = torch.zeros(16, dtype=torch.int64, device=dev) if is_src else None
     stamp_dst = torch.zeros(16, dtype=torch.int64, device=dev) if is_dst else None
-    stamp_layout = PairLayout(smesh, (Replicate(),), tmesh, (Replicate(),))
+    stamp_layout = PairLayout(smesh, (Replicate(),) * smesh.dim(), tmesh, (Replicate(),))
     ws = WeightSync(
-        model, rank, list(range(world)), dev, smesh, tmesh, fsdp_layout(), vllm_tp_layout(), exchange=exchange,
+        model, rank, list(range(world)), dev, smesh, tmesh, s_rule, t_rule, exchange=exchange,
+        source_dtype=getattr(torch, args.source_dtype), nvls=bool(args.nvls) and world > 1,
+        nvls_tag=f"bench{os.environ.get('MASTER_PORT', '0')}",
         extra=[(stamp_layout, stamp_src, stamp_dst)], tile_bytes=args.tile_kb * 1024,
         dma_min_bytes=args.dma_min_kb * 1024 if args.engine != "kernel" else None,
-        dma_mode="graph" if args.engine == "dma-graph" else "streams",
+        dma_mode="graph" if args.engine == "dma-graph" else "streams", dma_fraction=args.dma_fraction,
     ).build()
     # TMA bulk kernel by default when producer and consumer share the GPU (it only serves local destinations)
     bulk = bool(args.bulk) if args.bulk >= 0 else (world == 1)
@@ -179,6 +222,26 @@ def run_ours(args) -> dict:
     ms_step = ms_total / args.steps
     gbps = ws.payload_bytes / (ms_step * 1e-3) / 1e9
 
+    # ---- the same K steps with every copy in the kernels (no DMA engine), for the record ---------------------
+    kernels_only = None
+    if ws.batch.table.n_dma_copies or int(max_over_ranks(float(ws.batch.table.n_dma_copies), world)):
+        kw_k = dict(kw, dma=False)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record()
+        for _ in range(args.steps):
+            if world > 1:
+                dist.all_reduce(ready)
+            ws.sync(stream, timeout_s=20.0, **kw_k)
+        k1.record()
+        torch.cuda.synchronize()
+        ws.check()
+        k_ms = max_over_ranks(k0.elapsed_time(k1), world) / args.steps
+        kernels_only = {"ms_per_step": round(k_ms, 4), "value": round(ws.payload_bytes / (k_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
+                        "what": "same steps with dma=False: every copy issued by the sm_100a kernels"}
+
     # ---- end to end: pinned-host stamp upload, sync, stamp + status read back, host-visible completion ----
     pin_in = torch.zeros(16, dtype=torch.int64).pin_memory()
     pin_out = torch.zeros(16, dtype=torch.int64).pin_memory()
@@ -220,6 +283,15 @@ def run_ours(args) -> dict:
     if args.bus:
         bus = run_bus_e2e(args, rank, world, dev, ws, smesh, tmesh, stamp_src, stamp_dst, is_src, is_dst)
 
+    link_nominal, hbm_copy = 900e9, 6535e9
+    if world > 1:
+        roof_ms = busiest_bytes / link_nominal * 1e3
+        roof_what = "bytes the busiest GPU must send or receive / 900 GB/s (NVLink 5 nominal, one direction)"
+    else:
+        roof_ms = 2 * busiest_bytes / hbm_copy * 1e3
+        roof_what = "bytes read + written / measured HBM copy bandwidth (6535 GB/s)"
+    multicast_ops = int(max_over_ranks(float(ws.batch.multicast_ops), world))
+    ws.close()
     result = {
         "metric": METRIC,
         "value": round(gbps, 2),
@@ -239,8 +311,14 @@ def run_ours(args) -> dict:
             "global_batch": None,
             "seq_len": None,
             "parallelism": par,
+            "layout": args.layout,
+            "source_dtype": args.source_dtype,
             "tensors": len(model.tensors),
             "payload_bytes": ws.payload_bytes,
+            "roofline_ms": round(roof_ms, 4),
+            "roofline": roof_what,
+            "frac_of_roofline": round(roof_ms / ms_step, 3),
+            "nvls_multicast_ops": multicast_ops,
             "l2_policy": "inputs larger than L2 (16 GB per sync vs 126 MB)",
             "executor": "p2p copy table, " + ("TMA bulk kernel" if bulk else "LD/ST kernel")
                         + (f" + {ws.batch.table.n_dma_copies} DMA-engine copies ({args.engine})" if ws.batch.table.n_dma_copies else ""),
@@ -262,6 +340,7 @@ def run_ours(args) -> dict:
             "stamp_errors": stamp_errors,
         },
         "e2e_bus": bus,
+        "kernels_only": kernels_only,
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
@@ -305,9 +384,9 @@ def run_bus_e2e(args, rank, world, dev, ws, smesh, tmesh, stamp_src, stamp_dst, 
         return box[0]
 
     items = [BusItem(e.source, e.target, tuple(e.layout.source_placements), tuple(e.layout.target_placements)) for e in ws.entries]
-    items.append(BusItem(stamp_src, stamp_dst, (Replicate(),), (Replicate(),)))
-    src_agents = smesh.tolist() if world > 1 else [0]
-    dst_agents = tmesh.tolist() if world > 1 else [1]
+    items.append(BusItem(stamp_src, stamp_dst, (Replicate(),) * smesh.dim(), (Replicate(),)))
+    src_agents = smesh.reshape(-1).tolist() if world > 1 else [0]
+    dst_agents = tmesh.reshape(-1).tolist() if world > 1 else [1]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
     def stop():
@@ -318,7 +397,8 @@ def run_bus_e2e(args, rank, world, dev, ws, smesh, tmesh, stamp_src, stamp_dst, 
     out, failure = None, None
     try:
         out = bus_roundtrip(rank, world, dev.index, items, src_agents, dst_agents, steps=steps, warmup=2, share=share,
-                            on_step=on_step, timeout=150.0, timer=(e0.record, stop))
+                            on_step=on_step, timeout=150.0, timer=(e0.record, stop),
+                            source_mesh_shape=tuple(smesh.shape), target_mesh_shape=tuple(tmesh.shape))
     except Exception as e:  # reported, not fatal
         failure = f"{type(e).__name__}: {e}"[:300]
     ms = max_over_ranks(out["ms_per_step"] if out else float("inf"), world)

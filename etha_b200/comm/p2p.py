@@ -82,6 +82,7 @@ class P2PBatch:
         nvls=None,
         dma_min_bytes: int | None = None,
         dma_mode: str = "graph",
+        dma_fraction: float = 1.0,
     ):
         self.rank = rank
         self.ranks = list(ranks)
@@ -95,7 +96,7 @@ class P2PBatch:
         self.nvls = nvls
         # copies of at least `dma_min_bytes` whose destination is on another GPU are run by the DMA engines (a CUDA
         # graph of memcpy nodes built once, launched per transfer); None keeps every copy in the kernels
-        self.dma_min_bytes, self.dma_mode = dma_min_bytes, dma_mode
+        self.dma_min_bytes, self.dma_mode, self.dma_fraction = dma_min_bytes, dma_mode, dma_fraction
         self.multicast_ops = 0
         self.stripe_partial = True  # split the collapse of a Partial cell over the family members
         self._entries: list[tuple[PairLayout, torch.Tensor | None, torch.Tensor | None]] = []
@@ -147,7 +148,7 @@ class P2PBatch:
 
     def _finish_build(self, by_rank: dict[int, dict]) -> None:
         table = CopyTable(self.device, tile_bytes=self.tile_bytes, dma_min_bytes=getattr(self, "dma_min_bytes", None),
-                          dma_mode=getattr(self, "dma_mode", "graph"))
+                          dma_mode=getattr(self, "dma_mode", "graph"), dma_fraction=getattr(self, "dma_fraction", 1.0))
         my_gpu = by_rank[self.rank].get("gpu") if self.rank in by_rank else None
         consumers_i_write: set[int] = set()
         producers_i_wait: set[int] = set()
@@ -327,15 +328,17 @@ class P2PBatch:
         self.epoch += 1
         return self.epoch
 
-    def send(self, stream: torch.cuda.Stream | None = None, ctas_per_sm: int = 2, bulk: bool = False) -> None:
-        """Enqueue this rank's copies and the completion signal. Call `begin()` first."""
+    def send(self, stream: torch.cuda.Stream | None = None, ctas_per_sm: int = 2, bulk: bool = False,
+             dma: bool | None = None) -> None:
+        """Enqueue this rank's copies and the completion signal. Call `begin()` first.  `dma=False` keeps every copy
+        in the kernels for this transfer even when the batch was built with a DMA plan."""
         if self.table is None:
             raise RuntimeError("build() first")
         if self._signals is None and self.table.empty:
             return
         # `bulk`: run the 16-byte bit copies through the TMA ring kernel (local loads, plain bulk stores to local or
         # peer memory) instead of the LD/ST kernel
-        self.table.launch(stream, self._signals, self.epoch, ctas_per_sm=ctas_per_sm, bulk=bulk)
+        self.table.launch(stream, self._signals, self.epoch, ctas_per_sm=ctas_per_sm, bulk=bulk, dma=dma)
 
     def recv(self, stream: torch.cuda.Stream | None = None, timeout_s: float = 10.0) -> None:
         """Enqueue the bounded wait for every producer that writes into this rank."""

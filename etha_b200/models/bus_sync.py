@@ -66,6 +66,8 @@ def bus_roundtrip(
     device_type: str = "cuda",
     timeout: float = 120.0,
     timer: tuple[Callable[[], None], Callable[[], float]] | None = None,
+    source_mesh_shape: Sequence[int] | None = None,
+    target_mesh_shape: Sequence[int] | None = None,
 ) -> dict:
     """Time `steps` sync rounds through the bus.  Returns `{"ms_per_step": wall ms on this process, ...}`.
 
@@ -99,6 +101,10 @@ def bus_roundtrip(
             cq, st = paths(a)
             clients[a] = TensorBusClient(a, cq, st, connection_timeout=left())
         smesh, tmesh = torch.tensor(list(source_agent_ranks)), torch.tensor(list(target_agent_ranks))
+        if source_mesh_shape is not None:
+            smesh = smesh.view(tuple(source_mesh_shape))
+        if target_mesh_shape is not None:
+            tmesh = tmesh.view(tuple(target_mesh_shape))
         names: dict[tuple, str] = {}
         for it in items:
             names.setdefault((tuple(it.source_placements), tuple(it.target_placements)), f"pair{len(names)}")

@@ -89,6 +89,7 @@ class WeightSync:
         nvls_tag: str = "ws",
         dma_min_bytes: int | None = None,
         dma_mode: str = "graph",
+        dma_fraction: float = 1.0,
     ):
         self.model, self.rank, self.device, self.seed = model, rank, torch.device(device), seed
         self.smesh, self.tmesh = mesh_tensor_of(source_mesh), mesh_tensor_of(target_mesh)
@@ -154,7 +155,7 @@ class WeightSync:
 
         kw = {} if tile_bytes is None else {"tile_bytes": tile_bytes}
         self.batch = P2PBatch(rank, ranks, self.device, exchange=exchange, peer=peer, nvls=self.team,
-                              dma_min_bytes=dma_min_bytes, dma_mode=dma_mode, **kw)
+                              dma_min_bytes=dma_min_bytes, dma_mode=dma_mode, dma_fraction=dma_fraction, **kw)
         for e in self.entries:
             self.batch.add(e.layout, e.source, e.target)
         for layout, s, t in extra:

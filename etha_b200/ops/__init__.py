@@ -32,9 +32,8 @@ def local_copy(src: torch.Tensor, dst: torch.Tensor, stream: torch.cuda.Stream |
     t.finalize()
     t.launch(stream)
     # the table's device arrays must outlive the kernel: tie them to the stream
-    for buf in (*t._ops_dev, *t._tiles_dev, t._sync):
-        if buf is not None:
-            buf.record_stream(stream or torch.cuda.current_stream(dst.device))
+    for buf in t.device_buffers():
+        buf.record_stream(stream or torch.cuda.current_stream(dst.device))
 
 
 def set_flags(addresses: torch.Tensor, epoch: int, stream: torch.cuda.Stream | None = None) -> None:

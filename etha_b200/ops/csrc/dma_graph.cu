@@ -31,6 +31,8 @@ struct DmaPlan {
   std::vector<cudaStream_t> streams;  // stream fallback: copies are dealt round-robin over these
   std::vector<cudaEvent_t> done;
   cudaEvent_t fork = nullptr;
+  cudaStream_t branch = nullptr;  // the graph runs here so that kernels on the caller's stream overlap with it
+  cudaEvent_t joined = nullptr;
 };
 
 void destroy(DmaPlan* p) {
@@ -40,6 +42,8 @@ void destroy(DmaPlan* p) {
   for (auto e : p->done) cudaEventDestroy(e);
   for (auto s : p->streams) cudaStreamDestroy(s);
   if (p->fork) cudaEventDestroy(p->fork);
+  if (p->joined) cudaEventDestroy(p->joined);
+  if (p->branch) cudaStreamDestroy(p->branch);
   delete p;
 }
 
@@ -71,7 +75,10 @@ int etha_dma_plan_create(const EthaDmaCopy* copies, uint32_t n, int use_graph, i
   *out = nullptr;
   DmaPlan* p = new DmaPlan();
   p->copies.assign(copies, copies + n);
-  cudaError_t e;
+  cudaError_t e = cudaEventCreateWithFlags(&p->fork, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->joined, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&p->branch, cudaStreamNonBlocking);
+  if (e != cudaSuccess) { destroy(p); return fail(e, "branch stream of the copy plan"); }
   if (use_graph) {
     e = cudaGraphCreate(&p->graph, 0);
     if (e != cudaSuccess) { destroy(p); return fail(e, "cudaGraphCreate"); }
@@ -96,8 +103,6 @@ int etha_dma_plan_create(const EthaDmaCopy* copies, uint32_t n, int use_graph, i
   } else {
     if (n_streams < 1) n_streams = 1;
     if (n_streams > 32) n_streams = 32;
-    e = cudaEventCreateWithFlags(&p->fork, cudaEventDisableTiming);
-    if (e != cudaSuccess) { destroy(p); return fail(e, "cudaEventCreate"); }
     for (int k = 0; k < n_streams; ++k) {
       cudaStream_t s;
       cudaEvent_t ev;
@@ -113,18 +118,20 @@ int etha_dma_plan_create(const EthaDmaCopy* copies, uint32_t n, int use_graph, i
   return 0;
 }
 
-// Enqueues every copy of the plan after the work already on `stream`; work enqueued on `stream` afterwards
-// starts when all copies have completed.
+// Starts every copy of the plan after the work already on `stream`, on side streams: what the caller enqueues on
+// `stream` next (the copy kernels) runs concurrently with the DMA engines.  `etha_dma_plan_join` makes `stream`
+// wait for the copies; the completion flags are published after it.
 int etha_dma_plan_launch(void* plan, void* stream) {
   DmaPlan* p = static_cast<DmaPlan*>(plan);
   cudaStream_t s = (cudaStream_t)stream;
-  cudaError_t e;
+  cudaError_t e = cudaEventRecord(p->fork, s);
+  if (e != cudaSuccess) return fail(e, "cudaEventRecord");
   if (p->exec) {
-    e = cudaGraphLaunch(p->exec, s);
+    e = cudaStreamWaitEvent(p->branch, p->fork, 0);
+    if (e == cudaSuccess) e = cudaGraphLaunch(p->exec, p->branch);
+    if (e == cudaSuccess) e = cudaEventRecord(p->joined, p->branch);
     return e == cudaSuccess ? 0 : fail(e, "cudaGraphLaunch");
   }
-  e = cudaEventRecord(p->fork, s);
-  if (e != cudaSuccess) return fail(e, "cudaEventRecord");
   const size_t ns = p->streams.size();
   for (size_t k = 0; k < ns; ++k) {
     e = cudaStreamWaitEvent(p->streams[k], p->fork, 0);
@@ -143,10 +150,21 @@ int etha_dma_plan_launch(void* plan, void* stream) {
   }
   for (size_t k = 0; k < ns; ++k) {
     e = cudaEventRecord(p->done[k], p->streams[k]);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(s, p->done[k], 0);
-    if (e != cudaSuccess) return fail(e, "join of the copy streams");
+    if (e != cudaSuccess) return fail(e, "cudaEventRecord");
   }
   return 0;
+}
+
+int etha_dma_plan_join(void* plan, void* stream) {
+  DmaPlan* p = static_cast<DmaPlan*>(plan);
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t e = cudaSuccess;
+  if (p->exec) {
+    e = cudaStreamWaitEvent(s, p->joined, 0);
+  } else {
+    for (size_t k = 0; k < p->done.size() && e == cudaSuccess; ++k) e = cudaStreamWaitEvent(s, p->done[k], 0);
+  }
+  return e == cudaSuccess ? 0 : fail(e, "join of the copy streams");
 }
 
 int etha_dma_plan_destroy(void* plan) {

@@ -117,7 +117,8 @@ struct EthaDmaCopy {
 };
 int etha_op_dma_copies(const struct M2NOp* op, struct EthaDmaCopy* out);  // copies written (0: needs a kernel)
 int etha_dma_plan_create(const struct EthaDmaCopy* copies, uint32_t n, int use_graph, int n_streams, void** out);
-int etha_dma_plan_launch(void* plan, void* stream);
+int etha_dma_plan_launch(void* plan, void* stream);  // copies start after the work on `stream`, on side streams
+int etha_dma_plan_join(void* plan, void* stream);    // `stream` waits for them
 int etha_dma_plan_destroy(void* plan);
 
 // ---- IPC / device helpers ---------------------------------------------------------------------

@@ -92,6 +92,8 @@ def cuda_lib() -> C.CDLL:
         lib.etha_dma_plan_create.restype = i32
         lib.etha_dma_plan_launch.argtypes = [vp, vp]
         lib.etha_dma_plan_launch.restype = i32
+        lib.etha_dma_plan_join.argtypes = [vp, vp]
+        lib.etha_dma_plan_join.restype = i32
         lib.etha_dma_plan_destroy.argtypes = [vp]
         lib.etha_dma_plan_destroy.restype = i32
         lib.etha_enable_peer_access.argtypes = [i32]

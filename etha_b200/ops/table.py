@@ -52,19 +52,35 @@ class SliceRef:
         return SliceRef(view.data_ptr(), tuple(view.stride()), view.dtype, base, base + st.nbytes())
 
 
+class _KernelSet:
+    """Device arrays of the kernel classes for one set of ops."""
+
+    def __init__(self):
+        self.ops_dev: list[torch.Tensor | None] = [None, None]
+        self.tiles_dev: list[torch.Tensor | None] = [None, None]
+        self.tiles_rest_dev: torch.Tensor | None = None  # prefix sums of the fast ops the TMA kernel cannot run
+        self.n_ops, self.n_tiles = [0, 0], [0, 0]
+        self.n_bulk_ops = self.n_bulk_tiles = 0
+
+
 class CopyTable:
     """`dma_min_bytes`: when set, a bit copy of at least that many bytes whose box is one run or the rows of a matrix,
-    and which the caller marks `dma_ok` (its destination is on another GPU), is not packed for the kernels but
-    becomes a memcpy node of a CUDA graph run by the DMA engines (`dma_mode="graph"`), or an asynchronous copy on
-    one of `dma_streams` side streams (`dma_mode="streams"`)."""
+    and which the caller marks `dma_ok` (its destination is on another GPU), is a candidate for the DMA engines: at
+    `finalize()` the largest candidates, up to `dma_fraction` of the bytes the table delivers, become memcpy nodes
+    of a CUDA graph (`dma_mode="graph"`) or asynchronous copies on `dma_streams` side streams
+    (`dma_mode="streams"`); everything else is packed for the kernels.  At launch the copies run next to the
+    kernels: the DMA engines write larger NVLink packets than SM stores can, and the kernels fill the gaps
+    between consecutive DMA copies."""
 
     def __init__(self, device: torch.device | int | str, tile_bytes: int = DEFAULT_TILE_BYTES,
-                 dma_min_bytes: int | None = None, dma_mode: str = "graph", dma_streams: int = 8):
+                 dma_min_bytes: int | None = None, dma_mode: str = "graph", dma_streams: int = 8,
+                 dma_fraction: float = 1.0):
         self.device = torch.device(device) if not isinstance(device, torch.device) else device
         self.tile_bytes = int(tile_bytes)
         self.dma_min_bytes = dma_min_bytes
-        self.dma_mode, self.dma_streams = dma_mode, dma_streams
+        self.dma_mode, self.dma_streams, self.dma_fraction = dma_mode, dma_streams, dma_fraction
         self._dma: list[L.DmaCopy] = []
+        self._dma_candidates: list[tuple[int, int, list, tuple]] = []  # (bytes, position, copies, packed entry)
         self._dma_plan = None
         self.dma_bytes = 0
         self._lib = L.cuda_lib()
@@ -140,20 +156,21 @@ class CopyTable:
                 if rc != 0:
                     raise ValueError(f"cannot pack op ({rc}): {err.value.decode(errors='replace')}")
                 tiles = self._lib.etha_op_tiles(buf)
-                if tiles and dma_ok and self.dma_min_bytes is not None and numel * ddtype.itemsize >= self.dma_min_bytes:
-                    out = (L.DmaCopy * L.MAX_DST)()
-                    n = self._lib.etha_op_dma_copies(buf, out)
-                    if n > 0:
-                        for j in range(n):
-                            c = L.DmaCopy()
-                            C.memmove(C.byref(c), C.byref(out[j]), C.sizeof(L.DmaCopy))
-                            self._dma.append(c)
-                        self.dma_bytes += numel * ddtype.itemsize * n
-                        tiles = 0
                 if tiles:
                     cls = self._lib.etha_op_class(buf)
                     tma = cls == 0 and bool(self._lib.etha_op_bulk_ok(buf))
-                    self._packed.append((cls, tiles, buf.raw, tma))
+                    entry = (cls, tiles, buf.raw, tma)
+                    self._packed.append(entry)
+                    if dma_ok and self.dma_min_bytes is not None and numel * ddtype.itemsize >= self.dma_min_bytes:
+                        out = (L.DmaCopy * L.MAX_DST)()
+                        n = self._lib.etha_op_dma_copies(buf, out)
+                        if n > 0:
+                            copies = []
+                            for j in range(n):
+                                c = L.DmaCopy()
+                                C.memmove(C.byref(c), C.byref(out[j]), C.sizeof(L.DmaCopy))
+                                copies.append(c)
+                            self._dma_candidates.append((numel * ddtype.itemsize * n, len(self._packed) - 1, copies, entry))
                 self.payload_bytes += numel * ddtype.itemsize * len(part)
         self.read_bytes += numel * src0.dtype.itemsize * len(srcs)
 
@@ -169,15 +186,9 @@ class CopyTable:
         self.add(tuple(dst.shape), [SliceRef.of(s) for s in srcs], [SliceRef.of(dst)], sizes, ops)
 
     # ---- upload -----------------------------------------------------------------------------
-    def finalize(self, sm_count: int | None = None) -> "CopyTable":
-        if self._final:
-            return self
-        if sm_count is None:
-            sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
-        self.sm_count = sm_count
-        self._ops_dev: list[torch.Tensor | None] = [None, None]
-        self._tiles_dev: list[torch.Tensor | None] = [None, None]
-        self._tiles_rest_dev: torch.Tensor | None = None  # prefix sums of the fast ops the TMA kernel cannot run
+    def _upload(self, packed) -> "_KernelSet":
+        """Device arrays of one set of packed ops, split into the kernel classes."""
+        ks = _KernelSet()
 
         def prefix(tiles):
             starts = np.zeros(len(tiles) + 1, dtype=np.uint64)
@@ -186,25 +197,50 @@ class CopyTable:
                 raise ValueError("too many tiles in one table")
             return starts
 
-        def upload(starts):
+        def to_dev(starts):
             return torch.from_numpy(starts.astype(np.uint32).view(np.int32).copy()).to(self.device)
 
         for cls in (0, 1):
-            members = [(t, raw, tma) for c, t, raw, tma in self._packed if c == cls]
+            members = [(t, raw, tma) for c, t, raw, tma in packed if c == cls]
             if cls == 0:  # stable split: TMA-capable ops first, relative order kept inside both groups
                 members = [m for m in members if m[2]] + [m for m in members if not m[2]]
-                self.n_bulk_ops = sum(1 for m in members if m[2])
-                self.n_bulk_tiles = sum(m[0] for m in members if m[2])
-            self.n_ops[cls] = len(members)
+                ks.n_bulk_ops = sum(1 for m in members if m[2])
+                ks.n_bulk_tiles = sum(m[0] for m in members if m[2])
+            ks.n_ops[cls] = len(members)
             if not members:
                 continue
             starts = prefix([t for t, _, _ in members])
-            self.n_tiles[cls] = int(starts[-1])
+            ks.n_tiles[cls] = int(starts[-1])
             blob = np.frombuffer(b"".join(raw for _, raw, _ in members), dtype=np.uint8)
-            self._ops_dev[cls] = torch.from_numpy(blob.copy()).to(self.device)
-            self._tiles_dev[cls] = upload(starts)
-            if cls == 0 and 0 < self.n_bulk_ops < len(members):
-                self._tiles_rest_dev = upload(prefix([t for t, _, _ in members[self.n_bulk_ops:]]))
+            ks.ops_dev[cls] = torch.from_numpy(blob.copy()).to(self.device)
+            ks.tiles_dev[cls] = to_dev(starts)
+            if cls == 0 and 0 < ks.n_bulk_ops < len(members):
+                ks.tiles_rest_dev = to_dev(prefix([t for t, _, _ in members[ks.n_bulk_ops:]]))
+        return ks
+
+    def finalize(self, sm_count: int | None = None) -> "CopyTable":
+        if self._final:
+            return self
+        if sm_count is None:
+            sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.sm_count = sm_count
+        # the largest DMA candidates, up to the byte budget, leave the kernels' table
+        budget = self.dma_fraction * self.payload_bytes
+        taken: set[int] = set()
+        for nbytes, pos, copies, _ in sorted(self._dma_candidates, key=lambda c: (-c[0], c[1])):
+            if self.dma_bytes + nbytes > budget:
+                continue
+            taken.add(pos)
+            self.dma_bytes += nbytes
+        for nbytes, pos, copies, _ in self._dma_candidates:  # table order: the producers' rotation is kept
+            if pos in taken:
+                self._dma += copies
+        # two kernel sets share this table: every op (kernels only), and what is left next to the DMA copies
+        self._all = self._upload(self._packed)
+        self._rest = self._upload([e for i, e in enumerate(self._packed) if i not in taken]) if taken else self._all
+        self.n_ops, self.n_tiles = self._all.n_ops, self._all.n_tiles
+        self.n_bulk_ops, self.n_bulk_tiles = self._all.n_bulk_ops, self._all.n_bulk_tiles
+        self._dma_candidates = []
         self._sync = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._packed = []
         if self._dma:
@@ -231,7 +267,14 @@ class CopyTable:
 
     @property
     def empty(self) -> bool:
-        return self.n_tiles[0] + self.n_tiles[1] == 0 and not self._dma
+        return self.n_tiles[0] + self.n_tiles[1] == 0
+
+    def device_buffers(self) -> list[torch.Tensor]:
+        """Every device array a launch reads (callers that drop the table right after a launch tie these to the stream)."""
+        out = [self._sync]
+        for ks in {id(self._all): self._all, id(self._rest): self._rest}.values():
+            out += [b for b in (*ks.ops_dev, *ks.tiles_dev, ks.tiles_rest_dev) if b is not None]
+        return out
 
     # ---- launch -----------------------------------------------------------------------------
     def launch(
@@ -241,35 +284,42 @@ class CopyTable:
         epoch: int = 0,
         ctas_per_sm: int = 2,
         bulk: bool = False,
+        dma: bool | None = None,
     ) -> None:
-        """Enqueue the table on `stream`. `signals`: int64 device tensor of flag addresses to publish `epoch` to."""
+        """Enqueue the table on `stream`. `signals`: int64 device tensor of flag addresses to publish `epoch` to.
+        `bulk`: TMA ring kernel instead of the LD/ST kernel for the 16-byte bit copies; `dma=False`: every copy by
+        the kernels even if the table holds a DMA plan."""
         if not self._final:
             self.finalize()
         s = (stream or torch.cuda.current_stream(self.device)).cuda_stream
         n_sig = 0 if signals is None else signals.numel()
         sig_ptr = 0 if signals is None else signals.data_ptr()
+        dma = self._dma_plan is not None and dma is not False
+        ks = self._rest if dma else self._all
         # launches of this transfer: (kernel, ops, tile prefix sums, number of ops, tiles)
         plan = []
-        if self.n_tiles[0]:
-            ops0, tiles0 = self._ops_dev[0].data_ptr(), self._tiles_dev[0].data_ptr()
-            if bulk and self.n_bulk_tiles:
-                plan.append(("bulk", ops0, tiles0, self.n_bulk_ops, self.n_bulk_tiles))
-                rest = self.n_ops[0] - self.n_bulk_ops
+        if ks.n_tiles[0]:
+            ops0, tiles0 = ks.ops_dev[0].data_ptr(), ks.tiles_dev[0].data_ptr()
+            if bulk and ks.n_bulk_tiles:
+                plan.append(("bulk", ops0, tiles0, ks.n_bulk_ops, ks.n_bulk_tiles))
+                rest = ks.n_ops[0] - ks.n_bulk_ops
                 if rest:
-                    plan.append(("fast", ops0 + self.n_bulk_ops * self._op_size, self._tiles_rest_dev.data_ptr(), rest,
-                                 self.n_tiles[0] - self.n_bulk_tiles))
+                    plan.append(("fast", ops0 + ks.n_bulk_ops * self._op_size, ks.tiles_rest_dev.data_ptr(), rest,
+                                 ks.n_tiles[0] - ks.n_bulk_tiles))
             else:
-                plan.append(("fast", ops0, tiles0, self.n_ops[0], self.n_tiles[0]))
-        if self.n_tiles[1]:
-            plan.append(("general", self._ops_dev[1].data_ptr(), self._tiles_dev[1].data_ptr(), self.n_ops[1], self.n_tiles[1]))
-        dma = self._dma_plan is not None
+                plan.append(("fast", ops0, tiles0, ks.n_ops[0], ks.n_tiles[0]))
+        if ks.n_tiles[1]:
+            plan.append(("general", ks.ops_dev[1].data_ptr(), ks.tiles_dev[1].data_ptr(), ks.n_ops[1], ks.n_tiles[1]))
         if not plan or dma:
-            # with DMA copies in the transfer the kernels go first without a signal, then the copies, then the flags
-            for kernel, ops_ptr, tiles_ptr, n_ops, n_tiles in plan:
-                self._launch_kernel(kernel, ops_ptr, tiles_ptr, n_ops, n_tiles, ctas_per_sm, (sig_ptr, 0, 0, 0), s)
+            # with DMA copies in the transfer: the copies start on side streams, the kernels run next to them on
+            # the caller's stream without a signal, the stream then waits for the copies and the flags go last
             if dma:
                 L.check(self._lib.etha_dma_plan_launch(self._dma_plan, s), "dma launch")
                 DMA_COPY_COUNT[0] += len(self._dma)
+            for kernel, ops_ptr, tiles_ptr, n_ops, n_tiles in plan:
+                self._launch_kernel(kernel, ops_ptr, tiles_ptr, n_ops, n_tiles, ctas_per_sm, (sig_ptr, 0, 0, 0), s)
+            if dma:
+                L.check(self._lib.etha_dma_plan_join(self._dma_plan, s), "dma join")
             if n_sig:
                 L.check(self._lib.etha_set_flags(sig_ptr, n_sig, epoch & 0xFFFFFFFF, s), "set_flags")
                 LAUNCH_COUNT[0] += 1
