@@ -32,9 +32,10 @@ def peak_gbs() -> tuple[float, str]:
     return 6650.0, "fallback"
 
 
-def build_case(case: str, mb: int, dev, tile_kb: int):
+def build_case(case: str, mb: int, dev, tile_kb: int, streaming: bool = True):
     n_rows = mb * 1024 * 1024 // (4096 * 2)
     t = CopyTable(dev, tile_bytes=tile_kb * 1024)
+    t.stream_typed = streaming
     keep = []
     if case == "copy":
         src = torch.randn(n_rows, 4096, device=dev).to(torch.bfloat16)
@@ -88,13 +89,14 @@ def main():
     ap.add_argument("--tile-kb", type=int, default=64)
     ap.add_argument("--ctas-per-sm", type=int, default=2)
     ap.add_argument("--bulk", type=int, default=0)
+    ap.add_argument("--streaming", type=int, default=1, help="0: typed ops stay in the general kernel")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     peak, how = peak_gbs()
     cases = ["copy", "rows", "cvt", "reduce2", "reduce4", "fanout4"] if args.case == "all" else [args.case]
     for case in cases:
-        table, traffic, check, keep = build_case(case, args.mb, dev, args.tile_kb)
+        table, traffic, check, keep = build_case(case, args.mb, dev, args.tile_kb, bool(args.streaming))
         for _ in range(args.warmup):
             table.launch(ctas_per_sm=args.ctas_per_sm, bulk=bool(args.bulk))
         torch.cuda.synchronize()
@@ -114,6 +116,7 @@ def main():
             "case": case, "mb": args.mb, "bulk": args.bulk, "ms_median": round(med, 4), "ms_min": round(times[0], 4),
             "dram_traffic_GBps": round(gbs, 1), f"frac_of_{how}_copy_bw": round(gbs / peak, 3), "correct": ok,
             "tile_kb": args.tile_kb, "ctas_per_sm": args.ctas_per_sm,
+            "streaming_ops": getattr(table, "n_typed_ops", 0),
         }), flush=True)
         del table, keep
 

@@ -208,19 +208,31 @@ class P2PBatch:
         """Every copy of tensor `i`, for all ranks: `(executing rank, source ranks, source slices, box shape,
         [(consumer, slices)], family)`.
 
-        A plain route is executed by its producer.  A route of a Partial source is cut into one stripe per family
-        member along the first dimension that is long enough: member k collapses stripe k (reading the other members'
+        A plain route is executed by its producer.  Routes of a Partial source that collapse the same cell are merged
+        into one fan-out, which is then cut into one stripe per family member along the first dimension that is long enough: member k collapses stripe k (reading the other members'
         stripes over NVLink, its own locally, always in family order, so the result does not depend on who computes
         it) and stores it into the consumers.  Every member then moves 1/F of the cell instead of the primary moving
         all of it while the others idle."""
         smesh = mesh_tensor_of(layout.source_mesh)
         reductions, transfers = self._transfers_of(layout, i, by_rank)
         items = []
-        for primary, s_index, cshape, dst_list in transfers:
-            if not reductions:
+        if not reductions:
+            for primary, s_index, cshape, dst_list in transfers:
                 items.append((primary, (primary,), s_index, tuple(cshape), dst_list, None))
-                continue
+            return items
+        # Routes of a Partial source that collapse the same cell of the same family differ only in their consumer
+        # (the planner gives every replica of a Replicate target its own primary).  They are merged: the cell is
+        # collapsed once and the result stored into every consumer, so the contributors' shards cross NVLink once
+        # instead of once per replica.
+        merged: dict[tuple, list] = {}
+        for primary, s_index, cshape, dst_list in transfers:
             fam = partial_family(smesh, reductions, primary)
+            key = (fam.ranks, tuple((sl.start, sl.stop) for sl in s_index), tuple(cshape))
+            if key in merged:
+                merged[key][3].extend(dst_list)
+            else:
+                merged[key] = [primary, s_index, tuple(cshape), list(dst_list), fam]
+        for primary, s_index, cshape, dst_list, fam in merged.values():
             sdesc = by_rank[primary]["src"][i]
             for q in fam.ranks:
                 qdesc = by_rank[q]["src"][i]
@@ -229,7 +241,7 @@ class P2PBatch:
             n_members = len(fam.ranks)
             dim = next((d for d, n in enumerate(cshape) if n >= n_members), None) if self.stripe_partial else None
             if dim is None or n_members == 1:
-                items.append((primary, fam.ranks, s_index, tuple(cshape), dst_list, fam))
+                items.append((primary, fam.ranks, s_index, cshape, dst_list, fam))
                 continue
             extent = cshape[dim]
             for k, member in enumerate(fam.ranks):

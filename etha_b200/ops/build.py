@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 
-CUDA_SOURCES = ["m2n_kernels.cu", "m2n_bulk.cu", "dma_graph.cu", "table_pack.cpp", "ipc.cu", "vmm_arena.cpp"]
+CUDA_SOURCES = ["m2n_kernels.cu", "m2n_bulk.cu", "m2n_typed.cu", "dma_graph.cu", "table_pack.cpp", "ipc.cu", "vmm_arena.cpp"]
 HOST_SOURCES = ["psem.cpp", "shmq.cpp"]
 CUDA_LIB = os.path.join(HERE, "libetha_b200_cuda.so")
 HOST_LIB = os.path.join(HERE, "libetha_b200_host.so")

@@ -110,6 +110,16 @@ int etha_m2n_bulk_launch(const struct M2NOp* ops, const uint32_t* tile_start, ui
                          uint32_t* sync_scratch, const uint64_t* signals, uint32_t n_signals, uint32_t epoch,
                          int do_signal, void* stream);
 
+// Streaming class of the typed ops (m2n_typed.cu): conversions and single-level collapses of 2 or 4 sources over
+// one-run / matrix-row boxes in 8-element units, one kernel instance per key. `etha_op_stream_key` returns the key
+// of the instance that can run `op` ((src dtype << 8) | (dst dtype << 4) | sources) or 0; every op of a table
+// handed to `etha_m2n_typed_launch` must have that key. Other arguments as etha_m2n_launch.
+int etha_op_stream_key(const struct M2NOp* op);
+int etha_stream_ctas_per_sm(void);
+int etha_m2n_typed_launch(const struct M2NOp* ops, const uint32_t* tile_start, uint32_t n_ops, int key, int grid,
+                          uint32_t* sync_scratch, const uint64_t* signals, uint32_t n_signals, uint32_t epoch, int do_signal,
+                          void* stream);
+
 // ---- copy-engine lowering (dma_graph.cu) -------------------------------------------------------
 // One DMA copy: `height` rows of `width` bytes, `spitch` / `dpitch` bytes between rows (height 1: one run).
 struct EthaDmaCopy {

@@ -72,6 +72,11 @@ def cuda_lib() -> C.CDLL:
         lib.etha_general_ctas_per_sm.restype = i32
         lib.etha_op_bulk_ok.argtypes = [vp]
         lib.etha_op_bulk_ok.restype = i32
+        lib.etha_op_stream_key.argtypes = [vp]
+        lib.etha_op_stream_key.restype = i32
+        lib.etha_stream_ctas_per_sm.restype = i32
+        lib.etha_m2n_typed_launch.argtypes = [vp, vp, u32, i32, i32, vp, vp, u32, u32, i32, vp]
+        lib.etha_m2n_typed_launch.restype = i32
         lib.etha_m2n_launch.argtypes = [vp, vp, u32, i32, i32, i32, vp, vp, u32, u32, i32, vp]
         lib.etha_m2n_launch.restype = i32
         lib.etha_set_flags.argtypes = [vp, u32, u32, vp]

@@ -61,6 +61,8 @@ class _KernelSet:
         self.tiles_rest_dev: torch.Tensor | None = None  # prefix sums of the fast ops the TMA kernel cannot run
         self.n_ops, self.n_tiles = [0, 0], [0, 0]
         self.n_bulk_ops = self.n_bulk_tiles = 0
+        # streaming instances of the typed class: key -> (ops, tile prefix sums, number of ops, tiles)
+        self.typed: dict[int, tuple[torch.Tensor, torch.Tensor, int, int]] = {}
 
 
 class CopyTable:
@@ -85,7 +87,8 @@ class CopyTable:
         self.dma_bytes = 0
         self._lib = L.cuda_lib()
         self._op_size = self._lib.etha_sizeof_op()
-        self._packed: list[tuple[int, int, bytes, bool]] = []  # (class, tiles, op bytes, TMA-capable)
+        self._packed: list[tuple[int, int, bytes, bool, int]] = []  # (class, tiles, op bytes, TMA-capable, stream key)
+        self.stream_typed = True  # conversions / collapses over simple boxes use the streaming kernel instances
         self.payload_bytes = 0  # bytes delivered (destination side, all replicas)
         self.read_bytes = 0
         self._final = False
@@ -159,7 +162,8 @@ class CopyTable:
                 if tiles:
                     cls = self._lib.etha_op_class(buf)
                     tma = cls == 0 and bool(self._lib.etha_op_bulk_ok(buf))
-                    entry = (cls, tiles, buf.raw, tma)
+                    skey = self._lib.etha_op_stream_key(buf) if (cls == 1 and self.stream_typed) else 0
+                    entry = (cls, tiles, buf.raw, tma, skey)
                     self._packed.append(entry)
                     if dma_ok and self.dma_min_bytes is not None and numel * ddtype.itemsize >= self.dma_min_bytes:
                         out = (L.DmaCopy * L.MAX_DST)()
@@ -200,8 +204,14 @@ class CopyTable:
         def to_dev(starts):
             return torch.from_numpy(starts.astype(np.uint32).view(np.int32).copy()).to(self.device)
 
+        keys = list(dict.fromkeys(k for c, _, _, _, k in packed if c == 1 and k))
+        for key in keys:
+            members = [(t, raw) for c, t, raw, _, k in packed if c == 1 and k == key]
+            starts = prefix([t for t, _ in members])
+            blob = np.frombuffer(b"".join(raw for _, raw in members), dtype=np.uint8)
+            ks.typed[key] = (torch.from_numpy(blob.copy()).to(self.device), to_dev(starts), len(members), int(starts[-1]))
         for cls in (0, 1):
-            members = [(t, raw, tma) for c, t, raw, tma in packed if c == cls]
+            members = [(t, raw, tma) for c, t, raw, tma, k in packed if c == cls and not (c == 1 and k)]
             if cls == 0:  # stable split: TMA-capable ops first, relative order kept inside both groups
                 members = [m for m in members if m[2]] + [m for m in members if not m[2]]
                 ks.n_bulk_ops = sum(1 for m in members if m[2])
@@ -238,7 +248,12 @@ class CopyTable:
         # two kernel sets share this table: every op (kernels only), and what is left next to the DMA copies
         self._all = self._upload(self._packed)
         self._rest = self._upload([e for i, e in enumerate(self._packed) if i not in taken]) if taken else self._all
-        self.n_ops, self.n_tiles = self._all.n_ops, self._all.n_tiles
+        typed_ops = sum(v[2] for v in self._all.typed.values())
+        typed_tiles = sum(v[3] for v in self._all.typed.values())
+        # [fast class, typed + general]: the streaming instances count with the general class they were taken from
+        self.n_ops = [self._all.n_ops[0], self._all.n_ops[1] + typed_ops]
+        self.n_tiles = [self._all.n_tiles[0], self._all.n_tiles[1] + typed_tiles]
+        self.n_typed_ops = typed_ops
         self.n_bulk_ops, self.n_bulk_tiles = self._all.n_bulk_ops, self._all.n_bulk_tiles
         self._dma_candidates = []
         self._sync = torch.zeros(4, dtype=torch.int32, device=self.device)
@@ -274,6 +289,8 @@ class CopyTable:
         out = [self._sync]
         for ks in {id(self._all): self._all, id(self._rest): self._rest}.values():
             out += [b for b in (*ks.ops_dev, *ks.tiles_dev, ks.tiles_rest_dev) if b is not None]
+            for ops_t, tiles_t, _, _ in ks.typed.values():
+                out += [ops_t, tiles_t]
         return out
 
     # ---- launch -----------------------------------------------------------------------------
@@ -308,6 +325,8 @@ class CopyTable:
                                  ks.n_tiles[0] - ks.n_bulk_tiles))
             else:
                 plan.append(("fast", ops0, tiles0, ks.n_ops[0], ks.n_tiles[0]))
+        for key, (ops_t, tiles_t, n, tiles) in ks.typed.items():
+            plan.append((key, ops_t.data_ptr(), tiles_t.data_ptr(), n, tiles))
         if ks.n_tiles[1]:
             plan.append(("general", ks.ops_dev[1].data_ptr(), ks.tiles_dev[1].data_ptr(), ks.n_ops[1], ks.n_tiles[1]))
         if not plan or dma:
@@ -333,6 +352,9 @@ class CopyTable:
         if kernel == "bulk":
             rc = self._lib.etha_m2n_bulk_launch(ops_ptr, tiles_ptr, n_ops, min(n_tiles, self.sm_count),
                                                 self._sync.data_ptr(), *sig, s)
+        elif isinstance(kernel, int):  # key of a streaming instance
+            grid = min(n_tiles, self.sm_count * self._lib.etha_stream_ctas_per_sm())
+            rc = self._lib.etha_m2n_typed_launch(ops_ptr, tiles_ptr, n_ops, kernel, grid, self._sync.data_ptr(), *sig, s)
         else:
             general = kernel == "general"
             # the fast kernel is compiled for two 512-thread CTAs per SM; the general one reports its own occupancy

@@ -233,3 +233,67 @@ def test_tma_bulk_mixed_table_splits_per_op():
     assert torch.equal(d_wide, wide[:, 1024:2048])
     assert all(torch.equal(r, vec) for r in reps)
     assert torch.equal(d_narrow[:, 64:128], narrow[:, 64:128]) and int(d_narrow[:, :64].count_nonzero()) == 0
+
+
+@pytest.mark.parametrize("sdt,ddt", [
+    (torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32), (torch.float16, torch.bfloat16),
+    (torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16), (torch.float16, torch.float32),
+])
+@pytest.mark.parametrize("nsrc,opname", [(1, "sum"), (2, "sum"), (2, "avg"), (4, "sum"), (4, "max"), (2, "product"), (4, "min")])
+@pytest.mark.parametrize("rows", [False, True])
+def test_streaming_instances_equal_general_kernel(sdt, ddt, nsrc, opname, rows):
+    """The per-(dtype pair, source count) streaming kernels must give the general kernel's bits: same accumulation
+    order, same single rounding.  `rows`: source is a column block of a wider matrix (the matrix-row box form)."""
+    if nsrc == 1 and sdt == ddt:
+        pytest.skip("a same-dtype copy is a bit copy, not a typed op")
+    if nsrc > 1 and sdt != ddt and torch.float32 not in (sdt, ddt):
+        pytest.skip("collapses between the two 16-bit types have no streaming instance (general kernel)")
+    wide = [_rand((384, 1024), sdt, 300 + i) * 1.7 for i in range(nsrc)]
+    srcs = [w[:, 256:768] if rows else w[:, :512].contiguous() for w in wide]
+    outs = {}
+    for streaming in (True, False):
+        dsts = [torch.zeros(384, 512, dtype=ddt, device=DEV) for _ in range(2)]
+        t = CopyTable(DEV)
+        t.stream_typed = streaming
+        t.add((384, 512), [SliceRef.of(s) for s in srcs], [SliceRef.of(d) for d in dsts], (nsrc,) if nsrc > 1 else (),
+              (opname,) if nsrc > 1 else ())
+        t.finalize()
+        assert t.n_typed_ops == (1 if streaming else 0)
+        t.launch()
+        torch.cuda.synchronize()
+        assert t.error_word() == 0 and torch.equal(dsts[0], dsts[1])
+        outs[streaming] = dsts[0]
+    assert torch.equal(outs[True].view(torch.uint8), outs[False].view(torch.uint8))
+    if nsrc == 1:
+        assert torch.equal(outs[True], srcs[0].to(ddt))
+    else:
+        fam = PartialFamily(ranks=tuple(range(nsrc)), sizes=(nsrc,), ops=(opname,))
+        want = reduce_family_values([s.cpu() for s in srcs], fam, sdt).to(ddt)
+        assert torch.equal(outs[True].cpu(), want)
+
+
+def test_streaming_and_general_ops_share_one_table():
+    """A table with two streaming keys, a general-class op (3 sources) and bit copies: every class runs, the last
+    kernel publishes the flag."""
+    a32 = _rand((256, 512), torch.float32, 400)
+    b16 = [_rand((256, 512), torch.bfloat16, 401 + i) for i in range(3)]
+    raw = _rand((100, 64), torch.int32, 405)
+    o_cvt = torch.zeros(256, 512, dtype=torch.bfloat16, device=DEV)
+    o_red2 = torch.zeros(256, 512, dtype=torch.bfloat16, device=DEV)
+    o_red3 = torch.zeros(256, 512, dtype=torch.bfloat16, device=DEV)
+    o_raw = torch.zeros_like(raw)
+    flags = torch.zeros(1, dtype=torch.int32, device=DEV)
+    addrs = torch.tensor([flags.data_ptr()], dtype=torch.int64, device=DEV)
+    t = CopyTable(DEV)
+    t.add_copy(a32, o_cvt)
+    t.add_reduce(b16[:2], o_red2, (2,), ("sum",))
+    t.add_reduce(b16, o_red3, (3,), ("sum",))
+    t.add_copy(raw, o_raw)
+    t.finalize()
+    assert t.n_typed_ops == 2 and t.n_ops == [1, 3]
+    t.launch(signals=addrs, epoch=5)
+    torch.cuda.synchronize()
+    assert t.error_word() == 0 and flags.tolist() == [5]
+    assert torch.equal(o_cvt, a32.to(torch.bfloat16)) and torch.equal(o_raw, raw)
+    assert torch.equal(o_red2, (b16[0].float() + b16[1].float()).to(torch.bfloat16))
+    assert torch.equal(o_red3, ((b16[0].float() + b16[1].float()) + b16[2].float()).to(torch.bfloat16))

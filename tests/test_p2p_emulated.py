@@ -117,7 +117,7 @@ def test_tables_of_all_ranks_deliver_every_shard(case, overlap, monkeypatch):
 
     writers = {r: set() for r in ranks}
     for r, b in batches.items():
-        for cls, tiles, raw, _tma in b.table._packed:
+        for cls, tiles, raw, *_ in b.table._packed:
             op = OpView.from_buffer_copy(raw)
             assert op.mode == 0 and op.nsrc == 1
             src_rank, src_buf, src_base = world.buffer_of(op.src[0])
@@ -227,7 +227,7 @@ def test_typed_tables_convert_and_collapse(case, monkeypatch):
         b._entries = [(layout, None, None)]
         b._finish_build(by_rank)
         batches[r] = b
-        for cls, tiles, raw, _tma in b.table._packed:
+        for cls, tiles, raw, *_ in b.table._packed:
             op = OpView.from_buffer_copy(raw)
             if op.mode == 0:
                 for j in range(op.ndst):

@@ -85,7 +85,7 @@ def test_packed_ops_reproduce_strided_copies(seed):
     ev.copy_(sv)
     src_np = sp.contiguous().view(torch.uint8).numpy().reshape(-1)
     dst_np = dp.view(torch.uint8).numpy().reshape(-1)
-    for cls, tiles, raw, _tma in t._packed:
+    for cls, tiles, raw, *_ in t._packed:
         op = OpView.from_buffer_copy(raw)
         assert op.mode == 0
         _emulate(op, src_np, dst_np, sp.untyped_storage().data_ptr(), dp.untyped_storage().data_ptr())

@@ -26,7 +26,7 @@ def pack(shape, sstr, dstr, sdt=torch.bfloat16, ddt=torch.bfloat16, sptr=1 << 20
     srcs = [SliceRef(sptr + i * (1 << 30), tuple(sstr), sdt) for i in range(nsrc)]
     t.add(shape, srcs, [SliceRef(dptr, tuple(dstr), ddt)], **kw)
     assert len(t._packed) == 1
-    cls, tiles, raw, _tma = t._packed[0]
+    cls, tiles, raw, *_ = t._packed[0]
     return cls, tiles, OpView.from_buffer_copy(raw)
 
 
