@@ -268,3 +268,104 @@ def run(args, ref_dir: str) -> dict:
     }
     dist.destroy_process_group()
     return out if rank == 0 else {}
+
+
+def run_single(args, ref_dir: str) -> None:
+    """Single-tensor sweep through the reference's three methods, as its own benchmark runs them
+    (bench/transfer_benchmark.py:201-287, 339-378): chunk mode (`bucket_size=1`), 256 MiB buckets and
+    `gather_broadcast_comm`.  One bf16 `[rows, 4096]` tensor per case, producer mesh = first half of the ranks,
+    consumer mesh = second half.  Prints one JSON line per (layout, size) on rank 0; every time is the maximum over
+    ranks of a CUDA-event interval around `args.steps` back-to-back calls."""
+    import json
+
+    import torch
+    import torch.distributed as dist
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if root not in sys.path:
+        sys.path.insert(0, root)
+    _install_stubs()
+    sys.path.insert(0, ref_dir)
+    from bench import max_over_ranks
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world < 2:
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference cannot plan a transfer inside one rank"}))
+        return
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29534")
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    _arm_watchdog(rank, world, float(os.environ.get("ETHA_REFERENCE_LIMIT_S", "600")))
+    dist.init_process_group(backend="cuda:nccl,cpu:gloo", rank=rank, world_size=world)
+    from etha.comm import bucket_comm, chunk_to_bucket_ops, get_m2m_map, m2m_to_chunks
+    from etha.comm.comm_methods import gather_broadcast_comm
+    from torch.distributed.device_mesh import DeviceMesh
+    from torch.distributed.tensor import DTensor, distribute_tensor
+    from torch.distributed.tensor.placement_types import Replicate, Shard
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    k = world // 2
+    smesh = DeviceMesh("cuda", torch.arange(k))
+    tmesh = DeviceMesh("cuda", torch.arange(k, 2 * k))
+    is_src = rank < k
+    layouts = {"S0->S1": ((Shard(0),), (Shard(1),)), "S0->R": ((Shard(0),), (Replicate(),)), "R->S0": ((Replicate(),), (Shard(0),))}
+    maps = {}
+
+    def timed(fn) -> float:
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = max_over_ranks(e0.elapsed_time(e1), world) / args.steps
+        dist.barrier()
+        return ms
+
+    mb = args.min_mb
+    while mb <= args.max_mb:
+        rows = max(mb * 2**20 // (4096 * 2) // (8 * k) * (8 * k), 8 * k)
+        nbytes = rows * 4096 * 2
+        for lname, (sp, tp) in layouts.items():
+            if lname not in args.layouts.split(","):
+                continue
+            if lname not in maps:
+                maps[lname] = get_m2m_map(smesh, sp, tmesh, tp, group=dist.group.WORLD, device="cpu")
+            g = torch.Generator(device=dev).manual_seed(1)
+            origin = torch.randn((rows, 4096), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+            src_dt = distribute_tensor(origin, smesh, sp) if is_src else None
+            tgt = None if is_src else torch.zeros_like(distribute_tensor(origin, tmesh, tp).to_local())
+            chunks = m2m_to_chunks(maps[lname], rank=rank, source_tensor=src_dt.to_local() if is_src else None, target_tensor=tgt)
+            out = {"impl": "reference", "case": f"{lname} {mb}MiB", "n_gpus": world, "payload_MB": None}
+            copies = k if lname == "S0->R" else 1
+            payload = nbytes * copies
+            for name, size in (("chunk", 1), ("bucket256MiB", 256 << 20)):
+                buckets = chunk_to_bucket_ops(chunks=chunks, bucket_size=size)
+                out[f"{name}_ms"] = round(timed(lambda: bucket_comm(buckets=buckets)), 4)
+            ok = True
+            if tgt is not None:
+                ok = torch.equal(tgt, distribute_tensor(origin, tmesh, tp).to_local())
+            res = [None]
+
+            def gb():
+                res[0] = gather_broadcast_comm(tmesh, tp, src_dt, origin, k)
+
+            out["gather_broadcast_ms"] = round(timed(gb), 4)
+            if tgt is not None and res[0] is not None:
+                ok = ok and torch.equal(tgt, res[0].to_local())
+            out["payload_MB"] = round(payload / 2**20, 1)
+            best = min(out["chunk_ms"], out["bucket256MiB_ms"])
+            out["best_GBps"] = round(payload / best / 1e6, 1)
+            out["methods_agree_bit_exact"] = bool(max_over_ranks(0.0 if ok else 1.0, world) == 0.0)
+            if rank == 0:
+                print(json.dumps(out), flush=True)
+            del origin, src_dt, tgt, chunks
+            torch.cuda.empty_cache()
+        mb *= 4
+    dist.destroy_process_group()

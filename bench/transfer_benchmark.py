@@ -45,7 +45,8 @@ _CASE = [0]  # every rank runs the cases in the same order, so the counter names
 def run_case(name, model, smesh, tmesh, s_rule, t_rule, args, rank, world, exchange, busiest_bytes, partial=False):
     dev = torch.device("cuda", torch.cuda.current_device())
     ws = WeightSync(model, rank, list(range(world)), dev, smesh, tmesh, s_rule, t_rule, exchange=exchange,
-                    nvls=bool(args.nvls) and world > 1, nvls_tag=f"tb{os.environ.get('MASTER_PORT', '0')}_{_CASE[0]}").build()
+                    nvls=bool(args.nvls) and world > 1, nvls_tag=f"tb{os.environ.get('MASTER_PORT', '0')}_{_CASE[0]}",
+                    dma_min_bytes=(1 << 20) if args.engine == "dma-graph" else None, dma_fraction=0.7).build()
     _CASE[0] += 1
     ready = torch.zeros(1, device=dev)
 
@@ -60,17 +61,27 @@ def run_case(name, model, smesh, tmesh, s_rule, t_rule, args, rank, world, excha
         torch.cuda.synchronize()
         ws.check()
         bad = int(max_over_ranks(float(ws.verify() if args.verify else 0), world))
+        ws.rescale_sources(0.5)  # the check after the timed loop can only pass if the timed transfers delivered the data
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            step()
-        e1.record()
-        torch.cuda.synchronize()
+        from etha_b200.utils.profiling import ProfilingSpec, maybe_enable_profiling
+
+        spec = ProfilingSpec(enable_profiling=bool(args.profile), dump_folder=os.path.join(ROOT, "gpurun_out", "traces"),
+                             save_traces_folder=name.replace(' ', '_').replace('>', ''),
+                             profile_freq=args.steps, warmup_steps=1, active_steps=max(args.steps - 2, 1))
+        with maybe_enable_profiling(spec, rank=rank) as prof:
+            e0.record()
+            for _ in range(args.steps):
+                step()
+                if prof is not None:
+                    prof.step()
+            e1.record()
+            torch.cuda.synchronize()
         ws.check()
         ms = max_over_ranks(e0.elapsed_time(e1), world) / args.steps
+        bad_after = int(max_over_ranks(float(ws.verify() if args.verify else 0), world))
         mc = int(max_over_ranks(float(ws.batch.multicast_ops), world))
     finally:
         ws.close()
@@ -82,6 +93,8 @@ def run_case(name, model, smesh, tmesh, s_rule, t_rule, args, rank, world, excha
             "frac_of_roofline_measured": round(roof * 1e3 / ms, 3),
             "frac_of_roofline_nominal": round(busiest_bytes / LINK_NOMINAL * 1e3 / ms, 3) if world > 1 else None,
             "multicast_ops": mc, "nvls": bool(args.nvls) and world > 1, "mismatching_tensors": bad if args.verify else None,
+            "verified_after_timed_region": (bad_after == 0) if args.verify else None, "engine": args.engine,
+            "under_profiler_not_a_benchmark_number": bool(args.profile),
         }), flush=True)
 
 
@@ -97,7 +110,19 @@ def main():
     ap.add_argument("--verify", type=int, default=1)
     ap.add_argument("--layouts", default="S0->S1,S0->R,R->S0", help="comma-separated subset for --config single")
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers (0: full model)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"],
+                    help="reference: the unmodified reference's chunk / bucket / gather-broadcast methods (--config single)")
+    ap.add_argument("--profile", type=int, default=0, help="1: wrap the timed steps in torch.profiler and write chrome traces")
+    ap.add_argument("--engine", default="kernel", choices=["kernel", "dma-graph"])
     args = ap.parse_args()
+    if args.impl == "reference":
+        if args.config != "single":
+            raise SystemExit("--impl reference covers --config single here; the model configurations run through bench.py --impl reference")
+        from baseline.reference_arm import REF_DIR
+        from baseline.reference_run import run_single
+
+        run_single(args, REF_DIR)
+        return
     rank, world, _ = init_dist(args.gpus)
 
     def exchange(obj):

@@ -22,6 +22,7 @@ import torch
 from .. import ops
 from ..ops.table import CopyTable, DEFAULT_TILE_BYTES
 from ..parallel.peer import PeerMemory, TensorDesc
+from ..utils.profiling import nvtx_range
 from .chunks import cell_slices, chunk_shape_of, padded_slicers
 from .ir import M2MMap, partial_family
 from .planner import mesh_tensor_of, plan_m2m
@@ -43,6 +44,8 @@ class PairLayout:
     target_placements: Sequence
     global_shape: Sequence[int] | None = None  # set it (or leave it to be inferred) for unevenly sharded tensors
     _plan: M2MMap | None = None
+    # no layout was declared: the k-th source rank sends its whole tensor to the k-th target rank (1-D rank lists)
+    plain: bool = False
 
     def plan(self) -> M2MMap:
         if self._plan is None:
@@ -126,8 +129,10 @@ class P2PBatch:
             "flags": self._describe(self._flags),
             "gpu": self._gpu_id(),
         }
-        everyone = self.exchange(mine)
-        self._finish_build({e["rank"]: e for e in everyone})
+        with nvtx_range("etha.p2p.exchange_descriptors"):
+            everyone = self.exchange(mine)
+        with nvtx_range("etha.p2p.build_table"):
+            self._finish_build({e["rank"]: e for e in everyone})
         return self
 
     def _gpu_id(self) -> str:
@@ -143,10 +148,19 @@ class P2PBatch:
         self._entries = [(layout, None, None) for layout in layouts]
         self._flags = flags
         self._status = torch.zeros(2, dtype=torch.int32, device=self.device)
-        self._finish_build(by_rank)
+        with nvtx_range("etha.p2p.build_table"):
+            self._finish_build(by_rank)
         return self
 
     def _finish_build(self, by_rank: dict[int, dict]) -> None:
+        # this batch is one user of every peer allocation its descriptors live in (released by `close`)
+        regions = {}
+        for entry in by_rank.values():
+            for d in list(entry.get("src") or []) + list(entry.get("dst") or []) + [entry.get("flags")]:
+                if d is not None:
+                    regions[(d.region.pid, d.region.handle, d.region.base)] = d.region
+        retain = getattr(self.peer, "retain", None)
+        self._retained = retain(regions.values()) if retain else []
         table = CopyTable(self.device, tile_bytes=self.tile_bytes, dma_min_bytes=getattr(self, "dma_min_bytes", None),
                           dma_mode=getattr(self, "dma_mode", "graph"), dma_fraction=getattr(self, "dma_fraction", 1.0))
         my_gpu = by_rank[self.rank].get("gpu") if self.rank in by_rank else None
@@ -167,7 +181,7 @@ class P2PBatch:
             # all of them would pour into the same GPU at the same time and share its ingress.  Rotate: producer
             # number p starts with consumer p, then p+1, ... (a permutation schedule over the NVSwitch).
             s_ranks, t_ranks = layout.source_ranks, layout.target_ranks
-            if self.rank in s_ranks and len(t_ranks) > 1:
+            if self.rank in s_ranks and len(t_ranks) > 1 and not layout.plain:
                 p, nt = s_ranks.index(self.rank), len(t_ranks)
                 mine.sort(key=lambda t: min((t_ranks.index(r) - p) % nt for r, _ in t[3]))
             for members, s_index, cshape, dst_list, fam in mine:
@@ -268,6 +282,16 @@ class P2PBatch:
         if len(s_shapes) != len(s_ranks) or len(t_shapes) != len(t_ranks):
             missing = [r for r in s_ranks if r not in s_shapes] + [r for r in t_ranks if r not in t_shapes]
             raise ValueError(f"tensor {i}: ranks {missing} registered no tensor for their side")
+        if layout.plain:
+            if len(s_ranks) != len(t_ranks):
+                raise ValueError(f"tensor {i}: whole-tensor transfer needs equally many ranks on both sides")
+            out = []
+            for s, t in zip(s_ranks, t_ranks):
+                if s_shapes[s] != t_shapes[t]:
+                    raise ValueError(f"tensor {i}: rank {s} holds {s_shapes[s]} but its peer {t} expects {t_shapes[t]}")
+                full = tuple(slice(0, n) for n in s_shapes[s])
+                out.append((s, full, s_shapes[s], [(t, full)]))
+            return [], out
         m2m = layout.plan()
         out = []
         even = layout.global_shape is None
@@ -350,13 +374,15 @@ class P2PBatch:
             return
         # `bulk`: run the 16-byte bit copies through the TMA ring kernel (local loads, plain bulk stores to local or
         # peer memory) instead of the LD/ST kernel
-        self.table.launch(stream, self._signals, self.epoch, ctas_per_sm=ctas_per_sm, bulk=bulk, dma=dma)
+        with nvtx_range("etha.p2p.launch_copies"):
+            self.table.launch(stream, self._signals, self.epoch, ctas_per_sm=ctas_per_sm, bulk=bulk, dma=dma)
 
     def recv(self, stream: torch.cuda.Stream | None = None, timeout_s: float = 10.0) -> None:
         """Enqueue the bounded wait for every producer that writes into this rank."""
         if self._wait_slots is None:
             return
-        ops.wait_flags(self._flags, self._wait_slots, self.epoch, self._status, timeout_s, stream)
+        with nvtx_range("etha.p2p.launch_wait"):
+            ops.wait_flags(self._flags, self._wait_slots, self.epoch, self._status, timeout_s, stream)
 
     def check(self) -> None:
         """After a stream synchronize: raise if the wait timed out or a kernel reported a bad op."""
@@ -377,6 +403,16 @@ class P2PBatch:
     @property
     def payload_bytes(self) -> int:
         return self.table.payload_bytes if self.table is not None else 0
+
+    def close(self) -> None:
+        """Give up this batch's use of the peers' allocations (mappings no other batch uses are closed) and drop the
+        copy table.  Call it only when none of the batch's kernels is in flight."""
+        keys, self._retained = getattr(self, "_retained", []), []
+        if keys:
+            self.peer.release(keys)
+        self.table = None
+        self._signals = self._wait_slots = None
+        self._built = False
 
 
 def link_local(batches: Sequence[P2PBatch]) -> None:

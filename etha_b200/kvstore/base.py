@@ -108,18 +108,41 @@ class KVStore(ABC):
                 raise TimeoutError(f"Timeout waiting for {expected_count} keys matching '{key_pattern}', got {len(found)}")
             time.sleep(self.poll_interval)
 
-    # ---- rendezvous of a known set of ranks (the agents' pre-transfer barrier) ---------------------------
-    def barrier_arrive(self, key_prefix: str, rank: int, *, component: str | None = None) -> None:
-        """Announce `rank` at the barrier named `key_prefix`. Backends with atomic counters override this."""
-        self.set(f"{key_prefix}/rank:{rank}", "1", component=component)
+    # ---- counters and the reusable rendezvous of a known set of ranks ---------------------------------
+    def counter_add(self, key: str, amount: int = 1, *, component: str | None = None) -> int:
+        """Add to an integer key and return the new value.  This default is only safe when one writer owns the
+        key; backends with an atomic add override it."""
+        raw = self.try_get(key, component=component)
+        value = (int(raw.decode()) if raw else 0) + amount
+        if amount:
+            self.set(key, str(value), component=component)
+        return value
 
-    def barrier_count(self, key_prefix: str, ranks: list[int], *, component: str | None = None) -> int:
-        """How many of `ranks` have arrived (one poll, no waiting)."""
-        cands = [f"{key_prefix}/rank:{r}" for r in ranks]
-        return len(self.poll_keys(f"{key_prefix}/rank:*", "1", cands, component=component))
+    def mark_reached(self, key_prefix: str, rank: int, n: int, *, component: str | None = None) -> None:
+        """Record that `rank` has reached step `n` of the progress named `key_prefix` (one key per rank, overwritten)."""
+        self.set(f"{key_prefix}/rank:{rank}", str(n), component=component)
+
+    def count_reached(self, key_prefix: str, ranks: list[int], n: int, *, component: str | None = None) -> int:
+        """How many of `ranks` have reached step `n` (one poll, no waiting); any subset of the ranks may be asked."""
+        count = 0
+        for r in ranks:
+            raw = self.try_get(f"{key_prefix}/rank:{r}", component=component)
+            if raw and int(raw.decode()) >= n:
+                count += 1
+        return count
+
+    def barrier_arrive(self, key_prefix: str, rank: int, round_no: int = 1, *, component: str | None = None) -> None:
+        """Announce `rank` at round `round_no` (1, 2, ...) of the barrier named `key_prefix`.  The same keys are
+        reused by every round, so a barrier that runs once per transfer leaves a fixed number of keys behind.
+        Every round must be asked about with the same full list of participants."""
+        self.mark_reached(key_prefix, rank, round_no, component=component)
+
+    def barrier_count(self, key_prefix: str, ranks: list[int], round_no: int = 1, *, component: str | None = None) -> int:
+        """How many of `ranks` have reached round `round_no` (one poll, no waiting)."""
+        return self.count_reached(key_prefix, ranks, round_no, component=component)
 
     def barrier_forget(self, key_prefix: str, rank: int, *, component: str | None = None) -> None:
-        """Drop what `rank` left at a barrier every participant has passed."""
+        """Drop what `rank` left at a barrier that will not be used again."""
         self.delete(f"{key_prefix}/rank:{rank}", component=component)
 
     def try_get(self, key: str, *, component: str | None = None) -> bytes | None:

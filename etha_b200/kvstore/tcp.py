@@ -74,9 +74,19 @@ class TorchTCPStore(KVStore):
         k = self._prefixed(key, component)
         if not self._store.check([k]):
             return False
-        self._store.set(k, "")
+        try:
+            self._store.delete_key(k)
+        except Exception:  # a c10d store without delete: an empty value stands for "missing"
+            self._store.set(k, "")
         self._known_keys.discard(key)
         return True
+
+    def num_keys(self) -> int | None:
+        """Keys held by the server (all namespaces), where the store can tell."""
+        try:
+            return int(self._store.num_keys())
+        except Exception:
+            return None
 
     def set_bytes(self, key: str, data: bytes, *, component: str | None = None) -> None:
         self._store.set(self._prefixed(key, component), base64.b64encode(data).decode("ascii"))
@@ -93,15 +103,24 @@ class TorchTCPStore(KVStore):
             )
         return super().wait_for_keys(key_pattern, expected_count, value, timeout, candidate_keys, component=component)
 
-    # TCPStore has an atomic counter: a barrier costs one round trip per poll instead of two per participant
-    def barrier_arrive(self, key_prefix: str, rank: int, *, component: str | None = None) -> None:  # noqa: ARG002
+    # TCPStore has an atomic counter: a barrier costs one round trip per poll instead of two per participant, and
+    # one counter serves every round (round k is complete when it reaches k x participants)
+    def counter_add(self, key: str, amount: int = 1, *, component: str | None = None) -> int:
+        return int(self._store.add(self._prefixed(key, component), amount))
+
+    def barrier_arrive(self, key_prefix: str, rank: int, round_no: int = 1, *, component: str | None = None) -> None:  # noqa: ARG002
         self._store.add(self._prefixed(f"{key_prefix}/count", component), 1)
 
-    def barrier_count(self, key_prefix: str, ranks: list[int], *, component: str | None = None) -> int:  # noqa: ARG002
-        return int(self._store.add(self._prefixed(f"{key_prefix}/count", component), 0))
+    def barrier_count(self, key_prefix: str, ranks: list[int], round_no: int = 1, *, component: str | None = None) -> int:
+        done = int(self._store.add(self._prefixed(f"{key_prefix}/count", component), 0)) - (round_no - 1) * len(ranks)
+        return max(0, min(done, len(ranks)))
 
     def barrier_forget(self, key_prefix: str, rank: int, *, component: str | None = None) -> None:  # noqa: ARG002
-        return  # TCPStore cannot delete; one small counter per barrier is left behind
+        k = self._prefixed(f"{key_prefix}/count", component)
+        try:
+            self._store.delete_key(k)
+        except Exception:  # a c10d store without delete: one counter per barrier name is left behind
+            pass
 
     def close(self, cleanup: bool = True) -> None:  # noqa: ARG002
         self._store = None

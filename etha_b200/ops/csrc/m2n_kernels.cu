@@ -457,6 +457,15 @@ extern "C" int etha_m2n_run_noalloc(const M2NOpSpec* specs, uint32_t n_specs, in
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail(e, "cudaGetDevice");
+  // every call stages its tables from host arrays of the calling thread with asynchronous copies: recorded into a
+  // stream capture they would be replayed later from whatever those arrays hold then, so a capturing stream is refused
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  e = cudaStreamIsCapturing((cudaStream_t)stream, &cap);
+  if (e != cudaSuccess) return fail(e, "cudaStreamIsCapturing");
+  if (cap != cudaStreamCaptureStatusNone) {
+    snprintf(etha_err_buf(), ETHA_ERR_LEN, "the allocation-free entry point cannot be recorded into a stream capture");
+    return -101;
+  }
   unsigned char* scratch = nullptr;
   int sms = 0;
   int rc = noalloc_setup(dev, &scratch, &sms);

@@ -15,7 +15,10 @@
 //  * the array (ETHA_NOALLOC_SCRATCH_BYTES, 256-byte aligned) exists once per GPU that loads the library and
 //    stays resident until the process exits;
 //  * the first call on a device looks up the array's device address (no allocation, but a one-time runtime
-//    query); make that first call outside any stream capture;
+//    query);
+//  * never call it on a stream that is being captured, first call or later: each call copies its tables from
+//    host arrays that belong to the calling thread, which a captured copy would re-read at replay time.  The
+//    entry point checks and refuses a capturing stream (-101, nothing is enqueued);
 //  * every call rewrites the table and zeroes the counters before launching, so nothing depends on what the
 //    previous call left behind — but two calls that overlap on the GPU (different streams, different threads)
 //    share the array and race.  Serialise them, or use the table API, which owns its buffers;

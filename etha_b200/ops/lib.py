@@ -72,6 +72,10 @@ def cuda_lib() -> C.CDLL:
         lib.etha_general_ctas_per_sm.restype = i32
         lib.etha_op_bulk_ok.argtypes = [vp]
         lib.etha_op_bulk_ok.restype = i32
+        lib.etha_m2n_run_noalloc.argtypes = [C.POINTER(OpSpec), u32, i32, vp]
+        lib.etha_m2n_run_noalloc.restype = i32
+        lib.etha_m2n_noalloc_status.argtypes = [C.POINTER(u32), vp]
+        lib.etha_m2n_noalloc_status.restype = i32
         lib.etha_op_stream_key.argtypes = [vp]
         lib.etha_op_stream_key.restype = i32
         lib.etha_stream_ctas_per_sm.restype = i32

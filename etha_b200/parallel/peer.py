@@ -58,8 +58,17 @@ class TensorDesc:
         return _DTYPE_NAMES[self.dtype]
 
 
+class PeerExportError(RuntimeError):
+    """A tensor's memory cannot be shared with other processes."""
+
+
 class PeerMemory:
-    """Per-process registry of exported and mapped allocations."""
+    """Per-process registry of exported and mapped allocations.
+
+    Exported regions are remembered by base address but always carry the handle CUDA returned for the current
+    allocation; mappings of other processes' regions are keyed by `(owner pid, handle bytes)`, so an allocation
+    that was freed and re-created at the same address is opened afresh instead of reusing a dead mapping.
+    Mappings are reference counted by their users (`retain` / `release`): the last release closes the mapping."""
 
     def __init__(self, device: torch.device | int | None = None):
         if device is None:
@@ -68,8 +77,10 @@ class PeerMemory:
         self.pid = os.getpid()
         self._lib = L.cuda_lib()
         self._exported: dict[int, RegionDesc] = {}  # base -> desc
-        self._mapped: dict[tuple, int] = {}  # region key -> local base
-        self._keepalive: list[torch.Tensor] = []
+        self._mapped: dict[tuple, int] = {}  # map key -> local base
+        self._by_owner_base: dict[tuple, tuple] = {}  # (pid, device, base) -> map key of the current mapping
+        self._refs: dict[tuple, int] = {}  # map key -> users
+        self._keepalive: dict[int, torch.Tensor] = {}
         self._arenas: list = []  # VMM arenas of this process: their views are described without an IPC handle
 
     # ---- owner side -----------------------------------------------------------------------
@@ -86,13 +97,23 @@ class PeerMemory:
             handle = C.create_string_buffer(64)
             base, size = C.c_uint64(), C.c_uint64()
             storage_ptr = t.untyped_storage().data_ptr()
-            L.check(self._lib.etha_ipc_export(storage_ptr, handle, C.byref(base), C.byref(size)), "ipc_export")
+            rc = self._lib.etha_ipc_export(storage_ptr, handle, C.byref(base), C.byref(size))
+        if rc != 0:
+            raise PeerExportError(
+                f"cannot export the memory of a {tuple(t.shape)} {t.dtype} tensor on {t.device} for other processes "
+                f"({L.last_error()}). CUDA IPC handles exist only for plain cudaMalloc allocations: memory from "
+                "torch's expandable segments (PYTORCH_CUDA_ALLOC_CONF=expandable_segments:True), from a VMM pool "
+                "(cuMemCreate / cuMemMap) or from cudaMallocAsync cannot be exported this way. Allocate the registered "
+                "tensors with the default caching allocator, or place them in an etha_b200.parallel.arena.VmmArena "
+                "(shared by file descriptor)."
+            )
         region = self._exported.get(base.value)
-        if region is None or region.size != size.value:
+        if region is None or region.size != size.value or region.handle != handle.raw:
+            # first export of this address, or the allocation behind it was replaced: the fresh handle wins
             region = RegionDesc(self.pid, t.device.index, base.value, size.value, handle.raw)
             self._exported[base.value] = region
         if keepalive:
-            self._keepalive.append(t)
+            self._keepalive[id(t)] = t
         return TensorDesc(region, t.data_ptr() - base.value, tuple(t.shape), tuple(t.stride()),
                           str(t.dtype).replace("torch.", ""))
 
@@ -100,25 +121,76 @@ class PeerMemory:
         """Descriptor usable only inside this process (no IPC handle is created)."""
         st = t.untyped_storage()
         region = RegionDesc(self.pid, t.device.index if t.is_cuda else -1, st.data_ptr(), st.nbytes(), b"")
-        self._keepalive.append(t)
+        self._keepalive[id(t)] = t
         return TensorDesc(region, t.data_ptr() - st.data_ptr(), tuple(t.shape), tuple(t.stride()),
                           str(t.dtype).replace("torch.", ""))
 
+    def forget(self, tensors) -> None:
+        """Stop keeping `tensors` alive (their batch was cleaned up)."""
+        for t in tensors:
+            self._keepalive.pop(id(t), None)
+
     # ---- peer side ------------------------------------------------------------------------
+    @staticmethod
+    def _map_key(region: RegionDesc) -> tuple:
+        if region.handle and len(region.handle) == 64:
+            return (region.pid, region.handle)
+        return region.key  # VMM arena or test double: identified by owner and address
+
     def map_region(self, region: RegionDesc) -> int:
         """Address of `region.base` in this process (maps the allocation on first use)."""
         if region.pid == self.pid:
             return region.base
-        local = self._mapped.get(region.key)
+        key = self._map_key(region)
+        local = self._mapped.get(key)
         if local is None:
             if not region.handle or region.handle == b"vmm":
                 raise ValueError("region of another process has no IPC handle and no adopted mapping")
+            stale = self._by_owner_base.get(region.key)
+            if stale is not None and stale != key:
+                self._close(stale)  # the owner re-allocated this address: the old mapping points at freed memory
             with torch.cuda.device(self.device):
                 out = C.c_uint64()
                 L.check(self._lib.etha_ipc_open(region.handle, C.byref(out)), "ipc_open")
             local = out.value
-            self._mapped[region.key] = local
+            self._mapped[key] = local
+            self._by_owner_base[region.key] = key
         return local
+
+    def retain(self, regions) -> list[tuple]:
+        """Count one more user of the mappings of `regions` (mapping them if needed); returns the keys to hand
+        back to `release`."""
+        keys = []
+        for region in regions:
+            if region.pid == self.pid or not region.handle or len(region.handle) != 64:
+                continue
+            self.map_region(region)
+            key = self._map_key(region)
+            self._refs[key] = self._refs.get(key, 0) + 1
+            keys.append(key)
+        return keys
+
+    def release(self, keys) -> None:
+        """Drop one user per key; a mapping nobody uses any more is closed."""
+        for key in keys:
+            n = self._refs.get(key, 0) - 1
+            if n > 0:
+                self._refs[key] = n
+                continue
+            self._refs.pop(key, None)
+            self._close(key)
+
+    def _close(self, key: tuple) -> None:
+        local = self._mapped.pop(key, None)
+        if local is not None:
+            self._lib.etha_ipc_close(local)
+        for owner_base, k in list(self._by_owner_base.items()):
+            if k == key:
+                del self._by_owner_base[owner_base]
+
+    @property
+    def n_mapped(self) -> int:
+        return len(self._mapped)
 
     def adopt_mapping(self, region_key: tuple, local_base: int) -> None:
         """Register a mapping made elsewhere (a VMM arena imported from a file descriptor): descriptors whose
@@ -154,4 +226,6 @@ class PeerMemory:
         for local in self._mapped.values():
             self._lib.etha_ipc_close(local)  # mappings adopted from elsewhere are unknown to it and left alone
         self._mapped.clear()
+        self._by_owner_base.clear()
+        self._refs.clear()
         self._keepalive.clear()

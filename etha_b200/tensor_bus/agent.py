@@ -45,6 +45,7 @@ logger = logging.getLogger(__name__)
 
 TIME_INTERVAL = 0.001  # command-loop tick
 HEARTBEAT_PERIOD = 0.2
+ERROR_TTL_S = 120.0  # a failed command's message is kept this long for its client to read, then deleted
 
 _DTYPES = {str(d).replace("torch.", ""): d for d in [
     torch.float32, torch.float64, torch.float16, torch.bfloat16, torch.int8, torch.uint8, torch.int16, torch.int32,
@@ -116,6 +117,8 @@ class TensorBusAgent(AgentHandlers):
         self.pairs: dict[str, PairState] = {}
         self.batches: dict[str, BatchState] = {}
         self._jobs: list[_Job] = []
+        self._errors: list[tuple[float, str]] = []  # (time stored, semaphore name) of error keys in the state store
+        self.error_ttl_s = ERROR_TTL_S
         self._stop = threading.Event()
         self._peer = None
         self._hb = threading.Thread(target=self._heartbeat_loop, daemon=True)
@@ -162,6 +165,10 @@ class TensorBusAgent(AgentHandlers):
             time.sleep(block_s)
         for job in list(self._jobs):
             self._advance(job)
+        # clients open the state store read-only, so the agent removes error messages once they are old enough to
+        # have been read (the store has a fixed number of slots)
+        while self._errors and time.monotonic() - self._errors[0][0] > self.error_ttl_s:
+            self.state.delete(f"error:{self._errors.pop(0)[1]}")
         return bool(self._jobs)
 
     def _start(self, command) -> None:
@@ -190,6 +197,7 @@ class TensorBusAgent(AgentHandlers):
             logger.error("Agent %s: %s failed: %s\n%s", self.rank, type(job.command).__name__, e, traceback.format_exc())
             if job.command.semaphore_name:
                 self.state.set_error(job.command.semaphore_name, f"{type(e).__name__}: {e}")
+                self._errors.append((time.monotonic(), job.command.semaphore_name))
         self._jobs.remove(job)
         if job.command.semaphore_name:
             self._release_semaphore(job.command.semaphore_name)

@@ -6,10 +6,16 @@ them (src/etha/tensor_bus/agent.py:224-243, 450-455):
     pair:{p}/rank:{r}/{local_name}             "1"      this agent registered for side `local_name`
     pair:{p}/{local_name}/expected_world_size  int      ranks on that side
     pair:{p}/rank:{r}/mesh_shape | placements  pickles  layout of the side `r` belongs to
-    batch:{b}/rank:{r}/meta                    pickle   tensor descriptors + flag arrays of agent `r`   (new)
-    batch:{b}/go:{epoch}/rank:{r}              "1"      agent `r` entered transfer `epoch`               (new)
-    batch:{b}/done:{epoch}/rank:{r}            "1"      producer `r` finished its copies (host completion) (new)
+    batch:{b}/regs/rank:{r}                    int      how often agent `r` registered batch id `b`: the generation  (new)
+    batch:{b}/gen:{g}/rank:{r}/meta            pickle   tensor descriptors + flag arrays of agent `r`   (new)
+    batch:{b}/gen:{g}/go/...                   barrier  round k = every agent entered transfer k          (new)
+    batch:{b}/gen:{g}/done/rank:{r}            int      last transfer whose copies producer `r` finished (host completion) (new)
+    batch:{b}/gen:{g}/state:send_epoch         int      newest send, component `global`                   (new)
     batch:{b}/state:transfer_signal            "1"/"0"  component `global`
+
+Every key that belongs to one registration carries its generation `g`: registering the same batch id again (after a
+cleanup or a worker restart) never reads descriptors, barrier counts or epochs of the previous registration.  The
+barrier and completion keys are reused by every transfer, and `CleanupBatch` deletes what this agent wrote.
 """
 
 from __future__ import annotations
@@ -77,20 +83,33 @@ class AgentHandlers:
                 ms = store.get_bytes(f"pair:{pair}/rank:{r}/mesh_shape")
                 pl = store.get_bytes(f"pair:{pair}/rank:{r}/placements")
                 if ms and pl:
-                    infos.append((tuple(pickle.loads(ms)), tuple(pickle.loads(pl))))
+                    mesh = pickle.loads(ms)
+                    # newer clients send {"shape", "ids"} (the mesh's rank ids in mesh order); a bare shape tuple is
+                    # the reference's payload and means "ascending ranks, row-major"
+                    shape = tuple(mesh["shape"]) if isinstance(mesh, dict) else tuple(mesh)
+                    ids = tuple(mesh["ids"]) if isinstance(mesh, dict) and mesh.get("ids") is not None else None
+                    infos.append((shape, tuple(pickle.loads(pl)), ids))
             if not infos:
                 return None
             for i, info in enumerate(infos):
                 if info != infos[0]:
                     raise ValueError(f"pair '{pair}': rank {ranks[i]} declared {info}, rank {ranks[0]} declared {infos[0]}")
-            shape, plc = infos[0]
+            shape, plc, ids = infos[0]
             n = 1
             for s in shape:
                 n *= s
             if n != len(ranks):
                 raise ValueError(f"pair '{pair}': mesh shape {shape} does not hold {len(ranks)} ranks")
-            # the registered ranks, ascending, fill the mesh row-major (the reference assumes a contiguous range)
-            return torch.tensor(sorted(ranks)).view(shape), plc
+            agents = sorted(ranks)
+            if ids is None:
+                # the registered ranks, ascending, fill the mesh row-major (the reference assumes a contiguous range)
+                return torch.tensor(agents).view(shape), plc
+            # the worker's mesh names its ranks in its own numbering: the k-th smallest id is the worker attached to
+            # the k-th smallest agent rank of this side, and the mesh keeps the worker's order
+            if len(set(ids)) != n:
+                raise ValueError(f"pair '{pair}': the device mesh {ids} does not name {n} distinct ranks")
+            order = {wid: k for k, wid in enumerate(sorted(ids))}
+            return torch.tensor([agents[order[w]] for w in ids]).view(shape), plc
 
         local, remote = layout(local_ranks), layout(remote_ranks)
         st = PairState(
@@ -135,28 +154,34 @@ class AgentHandlers:
         for p, _, obj in entries:
             batch.pair_tensors.setdefault(p, []).append(obj)
         all_ranks = sorted(set(first.local_ranks) | set(first.remote_ranks))
+        if batch_id in self.batches:
+            self._drop_batch(self.batches.pop(batch_id))  # re-registration without a cleanup: release the old one first
+        # generation of this registration: every agent of the batch registers it the same number of times, and the
+        # count lives in the store, so it also survives an agent that was restarted in between
+        batch.gen = self.store.counter_add(f"batch:{batch_id}/regs/rank:{self.rank}", 1)
+        batch.key = f"batch:{batch_id}/gen:{batch.gen}"
 
         # publish what the other agents need, then wait for theirs
-        meta = {"rank": self.rank, "kind": kind, "local_name": first.local_name}
+        meta = {"rank": self.rank, "kind": kind, "local_name": first.local_name, "gen": batch.gen}
         if kind == "cuda":
             from ..parallel.peer import PeerMemory
 
             if self._peer is None:
                 self._peer = PeerMemory(self.device)
             flags = {d: torch.zeros(len(all_ranks), dtype=torch.int32, device=self.device) for d in ("fwd", "bwd")}
-            batch.keepalive.append(flags)
+            batch.flags = flags
             meta["descs"] = [obj for _, _, obj in entries]
             meta["flags"] = {d: self._peer.describe(t) for d, t in flags.items()}
             meta["gpu"] = str(torch.cuda.get_device_properties(self.device).uuid)
             meta["host"] = _hostname()
         else:
             meta["descs"] = [(tuple(t.shape), str(t.dtype).replace("torch.", "")) for _, _, t in entries]
-        self.store.set_bytes(f"batch:{batch_id}/rank:{self.rank}/meta", pickle.dumps(meta))
+        self.store.set_bytes(f"{batch.key}/rank:{self.rank}/meta", pickle.dumps(meta))
         metas = {}
         while len(metas) < len(all_ranks):
             for r in all_ranks:
                 if r not in metas:
-                    raw = self.store.get_bytes(f"batch:{batch_id}/rank:{r}/meta")
+                    raw = self.store.get_bytes(f"{batch.key}/rank:{r}/meta")
                     if raw:
                         metas[r] = pickle.loads(raw)
             if len(metas) < len(all_ranks):
@@ -165,6 +190,7 @@ class AgentHandlers:
             if len(m["descs"]) != len(entries) or m["kind"] != kind:
                 raise ValueError(f"Batch {batch_id}: rank {r} registered {len(m['descs'])} {m['kind']} tensors, "
                                  f"rank {self.rank} registered {len(entries)} {kind} tensors")
+        batch.kind = kind
         if kind == "cuda" and len({m.get("host") for m in metas.values()}) == 1:
             self._build_p2p(batch, entries, metas, all_ranks, flags)
         elif kind == "cuda":
@@ -239,6 +265,16 @@ class AgentHandlers:
             for pair_name, _, _ in entries:
                 ps = self.pairs[pair_name]
                 m = ps.m2m_send if sending else ps.m2m_recv
+                if m is None and ps.local_mesh is None and ps.remote_mesh is None:
+                    # no layout was declared for this pair: tensor i goes whole to the same-index rank of the other
+                    # side (reference fallback, src/etha/tensor_bus/agent.py:485-498), as one copy op per tensor
+                    src_ranks = sorted(batch.local_ranks if sending else batch.remote_ranks)
+                    dst_ranks = sorted(batch.remote_ranks if sending else batch.local_ranks)
+                    if len(src_ranks) != len(dst_ranks):
+                        raise ValueError(f"pair '{pair_name}' declared no layout and its sides have {len(src_ranks)} and "
+                                         f"{len(dst_ranks)} ranks: whole tensors can only go rank to rank")
+                    layouts.append(PairLayout(torch.tensor(src_ranks), None, torch.tensor(dst_ranks), None, plain=True))
+                    continue
                 if m is None:
                     ok = False
                     break
@@ -267,14 +303,14 @@ class AgentHandlers:
         # the device-side wait is used only when no other agent of the batch drives the same physical GPU:
         # two processes time-slicing one GPU must never have one kernel spin on a flag the other one sets
         mine = metas[self.rank]["gpu"]
-        batch.keepalive.append({"shared_gpu": sum(1 for r in all_ranks if metas[r]["gpu"] == mine) > 1})
+        batch.shared_gpu = sum(1 for r in all_ranks if metas[r]["gpu"] == mine) > 1
 
     # ---- Transfer -----------------------------------------------------------------------------------
-    def _store_barrier(self, key_prefix: str, ranks):
-        """All `ranks` set `{key_prefix}/rank:{r}`; yields until every key is there."""
+    def _store_barrier(self, key_prefix: str, ranks, round_no: int):
+        """Round `round_no` of the barrier `key_prefix` over `ranks`; yields until everybody has arrived."""
         ranks = list(ranks)
-        self.store.barrier_arrive(key_prefix, self.rank)
-        while self.store.barrier_count(key_prefix, ranks) < len(ranks):
+        self.store.barrier_arrive(key_prefix, self.rank, round_no)
+        while self.store.barrier_count(key_prefix, ranks, round_no) < len(ranks):
             yield
 
     def _transfer_job(self, msg: Transfer):
@@ -284,21 +320,24 @@ class AgentHandlers:
         sending = msg.transfer_type == "send"
         signal_key = f"batch:{batch.batch_id}/state:transfer_signal"
         if (batch.send_exec if sending else batch.recv_exec) is None:
-            raise RuntimeError(
-                f"Batch {batch.batch_id}: no {msg.transfer_type} plan. That direction has a Partial target, which is "
-                "not supported; Partial is only valid as a source placement."
-            )
+            partial_side = [p for p in batch.pair_names
+                            if any(isinstance(x, Partial) for x in ((self.pairs[p].remote_placements if sending
+                                                                      else self.pairs[p].local_placements) or ()))]
+            why = (f"pair(s) {partial_side} would have a Partial target in that direction, which is not supported "
+                   "(Partial is only valid as a source placement)" if partial_side else
+                   "no executor could be built for that direction when the batch was registered")
+            raise RuntimeError(f"Batch {batch.batch_id}: no {msg.transfer_type} plan: {why}.")
         batch.epoch += 1
         epoch = batch.epoch
         if sending and self.rank == batch.local_leader:
             # the epoch of the newest send is what receivers compare with the receives they have completed; the
             # "1"/"0" key of the reference is kept for observers but is not what `query_transfer_signal` reads,
             # because a late "0" of receive k can overwrite the "1" of send k+1
-            self.store.set(f"batch:{batch.batch_id}/state:send_epoch", str(epoch), component="global")
+            self.store.set(f"{batch.key}/state:send_epoch", str(epoch), component="global")
             self.store.set(signal_key, "1", component="global")
         all_ranks = sorted(set(batch.local_ranks) | set(batch.remote_ranks))
         # both sides meet here, like the reference's barrier on the batch group (agent.py:457)
-        yield from self._store_barrier(f"batch:{batch.batch_id}/go:{epoch}", all_ranks)
+        yield from self._store_barrier(f"{batch.key}/go", all_ranks, epoch)
 
         ex = batch.send_exec if sending else batch.recv_exec
         t0 = time.perf_counter()
@@ -310,9 +349,6 @@ class AgentHandlers:
             yield from self._p2p_transfer(batch, ex, sending, epoch)
         ms = (time.perf_counter() - t0) * 1e3
         self.state.put(f"batch:{batch.batch_id}/state:last_{msg.transfer_type}_ms", f"{ms:.3f}".encode())
-        if epoch > 2:  # the rendezvous keys of older epochs are dead: every rank has passed them
-            self.store.barrier_forget(f"batch:{batch.batch_id}/go:{epoch - 2}", self.rank)
-            self.store.delete(f"batch:{batch.batch_id}/done:{epoch - 2}/rank:{self.rank}")
         if not sending:
             batch.recv_done = epoch
             if self.rank == batch.local_leader:
@@ -323,29 +359,33 @@ class AgentHandlers:
         """Producers launch their copy table; every rank whose memory other ranks write (consumers) or read (Partial
         contributors) then waits until those ranks are done — on the device with the bounded flag wait, or through
         the KV store when another agent of the batch drives the same physical GPU."""
-        shared_gpu = any(isinstance(k, dict) and k.get("shared_gpu") for k in batch.keepalive)
+        from ..utils.profiling import nvtx_range
+
+        shared_gpu = batch.shared_gpu
         stream = torch.cuda.current_stream(self.device)
         ex.epoch = epoch - 1
         ex.begin()
-        done_prefix = f"batch:{batch.batch_id}/done:{epoch}"
+        done_prefix = f"{batch.key}/done"
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        if sending:
-            ex.send(stream)
-        waits_on_device = bool(ex._producers) and not shared_gpu
-        if waits_on_device:
-            ex.recv(stream, timeout_s=min(self.store_timeout, 60.0))
+        with nvtx_range(f"etha.transfer.{'send' if sending else 'recv'}.launch"):
+            if sending:
+                ex.send(stream)
+            waits_on_device = bool(ex._producers) and not shared_gpu
+            if waits_on_device:
+                ex.recv(stream, timeout_s=min(self.store_timeout, 60.0))
         e1.record(stream)
         while not e1.query():
             yield
         ex.check()
         if sending:
             self.state.put(f"batch:{batch.batch_id}/state:last_send_device_ms", f"{e0.elapsed_time(e1):.3f}".encode())
-            self.store.set(f"{done_prefix}/rank:{self.rank}", "1")  # own copies are complete: published before any wait
+            # own copies are complete: published (as "done up to this transfer") before any wait
+            self.store.mark_reached(done_prefix, self.rank, epoch)
+            batch.wrote_done = True
         if ex._producers and shared_gpu:
             producers = list(ex._producers)
-            cands = [f"{done_prefix}/rank:{r}" for r in producers]
-            while len(self.store.poll_keys(f"{done_prefix}/rank:*", "1", cands)) < len(producers):
+            while self.store.count_reached(done_prefix, producers, epoch) < len(producers):
                 yield
 
     def _plain_transfer(self, batch: BatchState, sending: bool):
@@ -368,14 +408,45 @@ class AgentHandlers:
             raise ValueError(f"QueryStatus for unknown batch: {msg.batch_id}")
         if msg.state_name != "transfer_signal":
             raise ValueError(f"Invalid state name: {msg.state_name}")
-        raw = self.store.try_get(f"batch:{msg.batch_id}/state:send_epoch", component="global")
-        pending = int(raw.decode()) > self.batches[msg.batch_id].recv_done if raw else False
+        batch = self.batches[msg.batch_id]
+        raw = self.store.try_get(f"{batch.key}/state:send_epoch", component="global")
+        pending = int(raw.decode()) > batch.recv_done if raw else False
         self.state.set_signal(msg.batch_id, msg.state_name, pending)
         return
         yield
 
     def _cleanup_batch_job(self, msg: CleanupBatch):
-        if self.batches.pop(msg.batch_id, None) is None:
+        batch = self.batches.pop(msg.batch_id, None)
+        if batch is None:
             logger.warning("Agent %s: cleanup for unknown batch %s", self.rank, msg.batch_id)
+        else:
+            self._drop_batch(batch)
         return
         yield
+
+    def _drop_batch(self, batch: BatchState) -> None:
+        """Release everything a registration holds: the executors' use of the peers' IPC mappings (a mapping no other
+        batch uses is closed), the flag arrays, and the keys this agent wrote for this generation."""
+        if self.device.type == "cuda" and (batch.send_exec is not None or batch.recv_exec is not None):
+            torch.cuda.synchronize(self.device)  # nothing of this batch may still be in flight
+        for ex in (batch.send_exec, batch.recv_exec):
+            if hasattr(ex, "close"):
+                ex.close()
+        batch.send_exec = batch.recv_exec = None
+        batch.send_buckets = batch.recv_buckets = None
+        if batch.flags and self._peer is not None:
+            self._peer.forget(batch.flags.values())
+        batch.flags = None
+        batch.pair_tensors.clear()
+        batch.keepalive.clear()
+        if batch.key:
+            self.store.delete(f"{batch.key}/rank:{self.rank}/meta")
+            self.store.barrier_forget(f"{batch.key}/go", self.rank)
+            if batch.wrote_done:
+                self.store.delete(f"{batch.key}/done/rank:{self.rank}")
+            if self.rank == batch.local_leader:
+                self.store.delete(f"{batch.key}/state:send_epoch", component="global")
+        self.state.delete(f"batch:{batch.batch_id}/state:transfer_signal")
+        for d in ("send", "recv"):
+            self.state.delete(f"batch:{batch.batch_id}/state:last_{d}_ms")
+        self.state.delete(f"batch:{batch.batch_id}/state:last_send_device_ms")

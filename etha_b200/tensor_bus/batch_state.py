@@ -24,3 +24,9 @@ class BatchState:
     epoch: int = 0
     recv_done: int = 0  # epoch of the last receive this agent completed
     keepalive: list = field(default_factory=list)
+    gen: int = 0  # how often this agent has registered this batch id; part of every key of the registration
+    key: str = ""  # "batch:{id}/gen:{gen}"
+    kind: str = ""  # "cuda" | "cpu"
+    flags: Any = None  # CUDA: {"fwd": int32[ranks], "bwd": ...} completion flags other agents write into
+    shared_gpu: bool = False  # another agent of the batch drives the same physical GPU: completion goes through the store
+    wrote_done: bool = False

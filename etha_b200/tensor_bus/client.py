@@ -98,9 +98,13 @@ class BatchHandler:
         if self._closed:
             return
         self._closed = True
-        self.client._execute_command_with_semaphore(
-            CleanupBatch(batch_id=self.batch_id), "cleanup_batch", f"batch_{self.batch_id}", blocking=blocking, timeout=timeout
-        )
+        client = self.client
+        try:
+            client._execute_command_with_semaphore(
+                CleanupBatch(batch_id=self.batch_id), "cleanup_batch", f"batch_{self.batch_id}", blocking=blocking, timeout=timeout
+            )
+        finally:
+            client._release_batch(self.batch_id)
 
     def __del__(self):
         try:
@@ -152,6 +156,7 @@ class TensorBusClient:
             lmdb_command_queue_path = os.environ.get("TENSOR_BUS_COMMAND_QUEUE_PATH")
         self.command_queue = CommandQueue(lmdb_command_queue_path)
         self._peer = None
+        self._keepalive: dict[str, list[torch.Tensor]] = {}
 
     # ---- plumbing ------------------------------------------------------------------------------
     def _raise_if_failed(self, sem_name: str, what: str) -> None:
@@ -208,8 +213,12 @@ class TensorBusClient:
         any order on the two sides and awaited afterwards (the agent progresses all handshakes concurrently)."""
         mesh_payload = placements_payload = None
         if device_mesh is not None:
-            shape = tuple(getattr(device_mesh, "mesh", device_mesh).shape)
-            mesh_payload = memoryview(pickle.dumps(tuple(int(s) for s in shape)))
+            m = getattr(device_mesh, "mesh", device_mesh)
+            shape = tuple(int(s) for s in m.shape)
+            # the shape is what the reference ships; the rank ids in mesh order let the agent honour a mesh whose
+            # ranks are not ascending (an agent that only knows the shape payload assumes ascending order)
+            ids = [int(x) for x in m.reshape(-1).tolist()] if hasattr(m, "reshape") else None
+            mesh_payload = memoryview(pickle.dumps({"shape": shape, "ids": ids}))
         if placements is not None:
             placements_payload = memoryview(pickle.dumps(tuple(placements)))
         msg = InitPair(pair_name=pair_name, local_name=local_name, expected_world_size=expected_world_size,
@@ -234,7 +243,8 @@ class TensorBusClient:
 
             self._peer = PeerMemory(next(t.device for t, _ in tensors if t.is_cuda))
         payload = [(pair, memoryview(encode_tensor(t, self._peer))) for t, pair in tensors]
-        self._keepalive = getattr(self, "_keepalive", []) + [t for t, _ in tensors]
+        # the registered tensors must outlive the registration: kept until the batch handler is closed
+        self._keepalive.setdefault(batch_id, []).extend(t for t, _ in tensors)
         msg = RegisterTensors(batch_id=batch_id, tensors=payload, bucket_size=bucket_size)
         done = self._execute_command_with_semaphore(msg, "register_tensors", f"batch_{batch_id}", blocking=blocking,
                                                     timeout=timeout)
@@ -253,7 +263,14 @@ class TensorBusClient:
         self._execute_command_with_semaphore(msg, "query", f"batch_{batch_id}", blocking=blocking, timeout=timeout)
         return self.state.signal(batch_id, "transfer_signal")
 
+    def _release_batch(self, batch_id: str) -> None:
+        """Stop pinning the tensors of a closed batch (and their IPC exports' keep-alive references)."""
+        tensors = self._keepalive.pop(batch_id, [])
+        if self._peer is not None and tensors:
+            self._peer.forget(tensors)
+
     def close(self) -> None:
+        self._keepalive.clear()
         self.command_queue.close(destroy=False)
         if self.state is not None:
             self.state.close()

@@ -107,11 +107,12 @@ class CommandQueue:
             except BusyError:
                 return None
         else:
+            # an item is taken only together with its semaphore count: a producer that has pushed but not yet posted
+            # delivers on the next call, and the count never runs ahead of the ring
             try:
                 self._sem.acquire(0)
             except BusyError:
-                if self._q.size() == 0:
-                    return None
+                return None
         data = self._q.pop()
         if data is None:
             return None

@@ -1,8 +1,6 @@
 """In-memory state of one registered pair on an agent (reference: src/etha/tensor_bus/pair_state.py:12-37)."""
 
 from dataclasses import dataclass
-from typing import Any
-
 import torch
 
 from ..comm.ir import M2MMap
@@ -24,7 +22,3 @@ class PairState:
     remote_placements: tuple | None = None
     m2m_send: M2MMap | None = None  # local -> remote
     m2m_recv: M2MMap | None = None  # remote -> local
-    # kept for field parity with the reference; no executor of this package needs process groups
-    local_group: Any = None
-    pair_group: Any = None
-    source_partial_groups: Any = None

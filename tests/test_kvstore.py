@@ -143,4 +143,14 @@ def test_barrier_helpers(store):
     store.barrier_arrive("b/go:1", 1)
     assert store.barrier_count("b/go:1", ranks) == 3
     assert store.barrier_count("b/go:2", ranks) == 0  # another barrier is independent
-    store.barrier_forget("b/go:1", 0)
+    # the same keys serve the next rounds: nothing new is left behind per round
+    assert store.barrier_count("b/go:1", ranks, 2) == 0
+    for r in ranks:
+        store.barrier_arrive("b/go:1", r, 2)
+    assert store.barrier_count("b/go:1", ranks, 2) == 3 and store.barrier_count("b/go:1", ranks, 1) == 3
+    assert store.barrier_count("b/go:1", ranks, 3) == 0
+    for r in ranks:
+        store.barrier_forget("b/go:1", r)
+    assert store.barrier_count("b/go:1", ranks) == 0
+    # counters
+    assert store.counter_add("b/gen") == 1 and store.counter_add("b/gen") == 2 and store.counter_add("b/gen", 0) == 2

@@ -252,3 +252,36 @@ def test_typed_tables_convert_and_collapse(case, monkeypatch):
             readers = {p for p in range(ns) if p != r and batches[p].table._packed and r in partial_family(smesh, red, p).ranks}
             assert readers <= set(batches[r]._producers)
             assert all(r in batches[p]._consumers for p in readers)
+
+
+def test_plain_layout_sends_whole_tensors_rank_to_rank(monkeypatch):
+    """No layout declared: the k-th producer's tensor goes whole into the k-th consumer's tensor, one op each."""
+    ranks = [0, 1, 2, 3]
+    world = World(ranks)
+    by_rank = {r: {"rank": r, "src": [None], "dst": [None]} for r in ranks}
+    sources, targets = {}, {}
+    for r in ranks:
+        if r < 2:
+            t, desc = world.alloc(r, (24, 10), torch.float32)
+            t.copy_(torch.randn(24, 10, generator=torch.Generator().manual_seed(r)))
+            by_rank[r]["src"], sources[r] = [desc], t
+        else:
+            t, desc = world.alloc(r, (24, 10), torch.float32)
+            by_rank[r]["dst"], targets[r] = [desc], t
+        _, by_rank[r]["flags"] = world.alloc(r, (len(ranks),), torch.int32)
+    monkeypatch.setattr(CopyTable, "finalize", lambda self, sm_count=None: self)
+    layout = PairLayout(torch.tensor([0, 1]), None, torch.tensor([2, 3]), None, plain=True)
+    for r in ranks:
+        b = P2PBatch.__new__(P2PBatch)
+        b.rank, b.ranks, b.device, b.peer = r, ranks, torch.device("cpu"), FakePeer(1000 + r)
+        b.nvls, b.tile_bytes, b.multicast_ops, b.stripe_partial = None, 4096, 0, True
+        b._entries = [(layout, None, None)]
+        b._finish_build(by_rank)
+        assert len(b.table._packed) == (1 if r < 2 else 0)
+        assert b._producers == ([r - 2] if r >= 2 else []) and b._consumers == ([r + 2] if r < 2 else [])
+        for cls, tiles, raw, *_ in b.table._packed:
+            op = OpView.from_buffer_copy(raw)
+            _, sbuf, sbase = world.buffer_of(op.src[0])
+            _, dbuf, dbase = world.buffer_of(op.dst[0])
+            _emulate(op, sbuf, dbuf, sbase, dbase)
+    assert torch.equal(targets[2], sources[0]) and torch.equal(targets[3], sources[1])
