@@ -325,7 +325,7 @@ class P2PBatch:
     def _add_multicast(self, table, shape, srcs, dst_ranks, by_rank, i, dsts, fam=None) -> bool:
         """Try to serve a fan-out route through the NVLS team; False means "use one store per replica"."""
         team = self.nvls
-        if team is None or len(dsts) < 2:
+        if team is None or len(dsts) < getattr(self, "multicast_min_replicas", 2):
             return False
         if set(dst_ranks) != set(getattr(team, "replicas", None) or team.ranks):
             return False

@@ -101,6 +101,30 @@ class VmmArena:
             _lib().etha_vmm_unmap_release(self.handle, self.va, self.size)
 
 
+class ImportedArena:
+    """Another process's `VmmArena`, mapped here from its file descriptor.  Has what `NvlsTeam` needs of an arena
+    (handle, address, size, a descriptor to pass on), so an agent can bind its worker's memory to a multicast object."""
+
+    def __init__(self, fd: int, size: int, device: torch.device | int):
+        self.device = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+        self.size, self.fd = int(size), int(fd)
+        with torch.cuda.device(self.device):
+            h, va = C.c_uint64(), C.c_uint64()
+            L.check(_lib().etha_vmm_import(self.fd, self.size, C.byref(h), C.byref(va)), "vmm_import")
+        self.handle, self.va = int(h.value), int(va.value)
+        self._closed = False
+        atexit.register(self.close)
+
+    def close(self) -> None:
+        if self._closed:
+            return
+        self._closed = True
+        _lib().etha_close_fd(self.fd)
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            _lib().etha_vmm_unmap_release(self.handle, self.va, self.size)
+
+
 def exchange_fds(rank: int, ranks: Sequence[int], fds: Sequence[int], tag: str, barrier: Callable[[], None],
                  directory: str = "/tmp") -> dict[int, list[int]]:
     """All-to-all hand-over of file descriptors between the processes `ranks` of one machine (SCM_RIGHTS over

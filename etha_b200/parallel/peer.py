@@ -52,6 +52,9 @@ class TensorDesc:
     shape: tuple[int, ...]
     strides: tuple[int, ...]  # elements
     dtype: str
+    # set for a view of a worker's replicated (VMM) arena: {"socket", "size", "pid", "device_index", "va"} tells the
+    # agent where to fetch the arena's file descriptor
+    arena: dict | None = None
 
     @property
     def torch_dtype(self) -> torch.dtype:

@@ -121,6 +121,7 @@ class TensorBusAgent(AgentHandlers):
         self.error_ttl_s = ERROR_TTL_S
         self._stop = threading.Event()
         self._peer = None
+        self._worker_arenas: dict[tuple, object] = {}  # (worker pid, address) -> imported replicated arena
         self._hb = threading.Thread(target=self._heartbeat_loop, daemon=True)
         self._hb.start()
         logger.info("Agent %s/%s up on %s, namespace %s", rank, world_size, self.device, store_namespace)
@@ -227,6 +228,14 @@ class TensorBusAgent(AgentHandlers):
     def close(self, destroy: bool = True) -> None:
         self._stop.set()
         self._hb.join(timeout=1.0)
+        for batch_id in list(self.batches):  # leave multicast teams and release mappings in order
+            try:
+                self._drop_batch(self.batches.pop(batch_id))
+            except Exception:
+                logger.exception("Agent %s: releasing batch %s failed", self.rank, batch_id)
+        for arena in self._worker_arenas.values():
+            arena.close()
+        self._worker_arenas.clear()
         self.command_queue.close(destroy=destroy)
         self.state.close()
         if destroy:

@@ -21,6 +21,7 @@ barrier and completion keys are reused by every transfer, and `CleanupBatch` del
 from __future__ import annotations
 
 import logging
+import os
 import pickle
 import time
 
@@ -172,7 +173,18 @@ class AgentHandlers:
             batch.flags = flags
             meta["descs"] = [obj for _, _, obj in entries]
             meta["flags"] = {d: self._peer.describe(t) for d, t in flags.items()}
+            # tensors the worker placed in its replicated (VMM) arena: fetch the arena once, tell the others its size
+            tickets = {(d.arena["pid"], d.arena["va"]): d.arena for _, _, d in entries if getattr(d, "arena", None)}
+            if len(tickets) > 1:
+                raise ValueError(f"Batch {batch_id}: tensors of {len(tickets)} replicated arenas; a worker has one")
+            if tickets:
+                ticket = next(iter(tickets.values()))
+                batch.arena = self._import_worker_arena(ticket)
+                meta["arena"] = {"size": ticket["size"], "key": (ticket["pid"], ticket["device_index"], ticket["va"])}
             meta["gpu"] = str(torch.cuda.get_device_properties(self.device).uuid)
+            from ..ops import device_info
+
+            meta["multicast"] = bool(device_info()["multicast"])
             meta["host"] = _hostname()
         else:
             meta["descs"] = [(tuple(t.shape), str(t.dtype).replace("torch.", "")) for _, _, t in entries]
@@ -192,6 +204,8 @@ class AgentHandlers:
                                  f"rank {self.rank} registered {len(entries)} {kind} tensors")
         batch.kind = kind
         if kind == "cuda" and len({m.get("host") for m in metas.values()}) == 1:
+            if any(m.get("arena") for m in metas.values()):
+                self._join_multicast_team(batch, metas, all_ranks)
             self._build_p2p(batch, entries, metas, all_ranks, flags)
         elif kind == "cuda":
             # the pair spans machines: peer pointers end at the NVLink domain, so fall back to the bucket executor
@@ -203,6 +217,7 @@ class AgentHandlers:
         else:
             self._build_buckets(batch, entries, metas)
         self.batches[batch_id] = batch
+        self.state.put(f"batch:{batch_id}/state:multicast_ops", str(batch.multicast_ops).encode())
         logger.info("Agent %s: batch %s registered (%d tensors, %s)", self.rank, batch_id, len(entries), kind)
 
     def _build_buckets(self, batch: BatchState, entries, metas) -> None:
@@ -295,8 +310,11 @@ class AgentHandlers:
                     "flags": metas[r]["flags"][direction],
                     "gpu": metas[r].get("gpu"),
                 }
-            b = P2PBatch(self.rank, all_ranks, self.device, peer=self._peer, use_ipc=True)
-            return b.build_from(layouts, by_rank, flags[direction])
+            b = P2PBatch(self.rank, all_ranks, self.device, peer=self._peer, use_ipc=True, nvls=batch.team)
+            b.multicast_min_replicas = int(os.environ.get("ETHA_NVLS_MIN_REPLICAS", "2"))
+            b.build_from(layouts, by_rank, flags[direction])
+            batch.multicast_ops += b.multicast_ops
+            return b
 
         batch.send_exec = build(send_dir, True)
         batch.recv_exec = build(recv_dir, False)
@@ -304,6 +322,85 @@ class AgentHandlers:
         # two processes time-slicing one GPU must never have one kernel spin on a flag the other one sets
         mine = metas[self.rank]["gpu"]
         batch.shared_gpu = sum(1 for r in all_ranks if metas[r]["gpu"] == mine) > 1
+
+    # ---- NVLS: replicated arenas of the workers bound to one multicast object --------------------------------
+    def _import_worker_arena(self, ticket: dict):
+        """Map the worker's replicated arena in this process: the file descriptor comes over the Unix socket the
+        worker's client serves (SCM_RIGHTS).  One import per arena; later batches reuse it."""
+        import socket
+
+        from ..parallel.arena import ImportedArena
+
+        key = (ticket["pid"], ticket["va"])
+        arena = self._worker_arenas.get(key)
+        if arena is None:
+            with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as c:
+                c.settimeout(10.0)
+                c.connect(ticket["socket"])
+                _msg, fds, _flags, _addr = socket.recv_fds(c, 16, 4)
+                c.send(b"k")
+            if not fds:
+                raise RuntimeError(f"the worker's arena socket {ticket['socket']} sent no file descriptor")
+            arena = ImportedArena(fds[0], ticket["size"], self.device)
+            self._worker_arenas[key] = arena
+            # descriptors of views of the arena name the worker's address range: resolve them to this mapping
+            self._peer.adopt_mapping((ticket["pid"], ticket["device_index"], ticket["va"]), arena.va)
+        return arena
+
+    def _kv_all_gather(self, batch: BatchState, ranks):
+        """`all_gather(obj)` over the KV store for the ranks of one batch (blocking, bounded by the store timeout):
+        what the multicast team construction uses as its exchange and barrier."""
+        seq = [0]
+
+        def all_gather(obj):
+            seq[0] += 1
+            prefix = f"{batch.key}/team/{seq[0]}"
+            self.store.set_bytes(f"{prefix}/rank:{self.rank}", pickle.dumps(obj))
+            batch.team_keys.append(f"{prefix}/rank:{self.rank}")
+            deadline = time.monotonic() + min(self.store_timeout, 120.0)
+            out = {}
+            while len(out) < len(ranks):
+                for r in ranks:
+                    if r not in out:
+                        raw = self.store.get_bytes(f"{prefix}/rank:{r}")
+                        if raw:
+                            out[r] = pickle.loads(raw)
+                if len(out) < len(ranks):
+                    if time.monotonic() > deadline:
+                        raise TimeoutError(f"multicast team of batch {batch.batch_id}: ranks {sorted(set(ranks) - set(out))} did not answer")
+                    time.sleep(0.001)
+            return [out[r] for r in ranks]
+
+        return all_gather
+
+    def _join_multicast_team(self, batch: BatchState, metas, all_ranks) -> None:
+        """Every agent of the batch joins one NVLS team: consumers whose workers registered tensors of a replicated
+        arena bind that arena, everybody else binds a scratch arena of the same size (every member device of a
+        multicast object must have memory bound).  Any obstacle (no multicast support, arenas of different sizes)
+        leaves `batch.team` unset and the fan-out falls back to one peer store per replica."""
+        from ..ops import device_info
+        from ..parallel.arena import NvlsTeam, VmmArena
+
+        sizes = {m["arena"]["size"] for m in metas.values() if m.get("arena")}
+        supported = all(m.get("multicast", False) for m in metas.values())
+        if len(sizes) != 1 or not supported or not device_info()["multicast"]:
+            logger.warning("Agent %s: batch %s: no multicast team (arena sizes %s, multicast supported everywhere: %s)",
+                           self.rank, batch.batch_id, sorted(sizes), supported)
+            return
+        size = sizes.pop()
+        mine = batch.arena
+        if mine is None:
+            mine = batch.scratch_arena = VmmArena(size, self.device, n_team=len(all_ranks))
+            if mine.size != size:
+                raise ValueError(f"Batch {batch.batch_id}: replicated arenas of {size} bytes are not a multiple of the "
+                                 f"multicast granularity on this device ({mine.size} after rounding)")
+        team = NvlsTeam(self.rank, all_ranks, mine, f"{self.namespace}_{batch.batch_id}_{batch.gen}".replace("/", "_"),
+                        self._kv_all_gather(batch, all_ranks))
+        team.replicas = sorted(r for r in all_ranks if metas[r].get("arena"))
+        for r in team.replicas:
+            if r != self.rank:  # views of a consumer's arena resolve to the mapping the team made of it
+                self._peer.adopt_mapping(tuple(metas[r]["arena"]["key"]), team.peer_va[r])
+        batch.team = team
 
     # ---- Transfer -----------------------------------------------------------------------------------
     def _store_barrier(self, key_prefix: str, ranks, round_no: int):
@@ -434,6 +531,16 @@ class AgentHandlers:
                 ex.close()
         batch.send_exec = batch.recv_exec = None
         batch.send_buckets = batch.recv_buckets = None
+        if batch.team is not None:  # leave the multicast team (unmap, unbind) before any arena goes away
+            batch.team.close()
+            batch.team = None
+        if batch.scratch_arena is not None:
+            batch.scratch_arena.close()
+            batch.scratch_arena = None
+        batch.arena = None  # an imported worker arena stays mapped for the next registration (closed with the agent)
+        for k in batch.team_keys:
+            self.store.delete(k)
+        batch.team_keys.clear()
         if batch.flags and self._peer is not None:
             self._peer.forget(batch.flags.values())
         batch.flags = None
@@ -450,3 +557,4 @@ class AgentHandlers:
         for d in ("send", "recv"):
             self.state.delete(f"batch:{batch.batch_id}/state:last_{d}_ms")
         self.state.delete(f"batch:{batch.batch_id}/state:last_send_device_ms")
+        self.state.delete(f"batch:{batch.batch_id}/state:multicast_ops")

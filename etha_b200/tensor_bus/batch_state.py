@@ -30,3 +30,9 @@ class BatchState:
     flags: Any = None  # CUDA: {"fwd": int32[ranks], "bwd": ...} completion flags other agents write into
     shared_gpu: bool = False  # another agent of the batch drives the same physical GPU: completion goes through the store
     wrote_done: bool = False
+    # NVLS: this agent's arena in the batch's multicast team (the worker's replicated arena, or scratch), the team
+    arena: Any = None
+    scratch_arena: Any = None
+    team: Any = None
+    team_keys: list = field(default_factory=list)
+    multicast_ops: int = 0  # ops of this agent's copy tables written with multimem.st

@@ -43,12 +43,17 @@ def generate_semaphore_name(command_type: str, context_id: str) -> str:
     return f"/command_{command_type}_{safe}_{os.getpid()}_{uuid.uuid4().hex}"
 
 
-def encode_tensor(t: torch.Tensor, peer=None) -> bytes:
-    """Serialise a handle to `t` for the agent (never the data)."""
+def encode_tensor(t: torch.Tensor, peer=None, arena=None) -> bytes:
+    """Serialise a handle to `t` for the agent (never the data).  A tensor inside the client's replicated arena
+    carries, next to its descriptor, where the agent can fetch the arena's file descriptor."""
     t = t.detach()
     if t.is_cuda:
         from ..parallel.peer import PeerMemory
 
+        if arena is not None and arena.contains(t):
+            import dataclasses
+
+            return pickle.dumps(("cuda", dataclasses.replace(arena.arena.describe(t), arena=arena.ticket())))
         peer = peer or PeerMemory(t.device)
         return pickle.dumps(("cuda", peer.describe(t)))
     # CPU: move the storage to a named shared-memory file any process can open
@@ -61,6 +66,83 @@ def encode_tensor(t: torch.Tensor, peer=None) -> bytes:
     manager, handle, size = t.untyped_storage()._share_filename_cpu_()
     meta = (manager, handle, size, t.storage_offset(), tuple(t.shape), tuple(t.stride()), str(t.dtype).replace("torch.", ""))
     return pickle.dumps(("cpu", meta))
+
+
+class ReplicatedArena:
+    """Worker-owned block of VMM device memory for tensors every consumer holds in full (Replicate targets).
+
+    Memory from `cudaMalloc` cannot be bound to an NVSwitch multicast object; this arena can.  The worker carves its
+    replicated tensors out of it (`TensorBusClient.empty_replicated`), the agent fetches the arena's file descriptor
+    once (a Unix socket next to the arena, `SCM_RIGHTS`), binds it into a multicast team with the other agents of the
+    batch, and producers then write all replicas with one `multimem.st` pass.  Every consumer must allocate the same
+    tensors in the same order, so that a tensor sits at the same offset in every replica's arena."""
+
+    def __init__(self, nbytes: int, device):
+        import socket
+        import tempfile
+        import threading
+
+        from ..parallel.arena import VmmArena
+
+        from ..ops import device_info
+
+        # sized in multiples of the multicast granularity, so that the agents can bind it to a multicast object
+        with torch.cuda.device(device):
+            multicast = device_info()["multicast"]
+        self.arena = VmmArena(nbytes, device, n_team=8 if multicast else 0)
+        self._cursor = 0
+        self._path = os.path.join(tempfile.gettempdir(), f"etha_arena_{os.getpid()}_{uuid.uuid4().hex[:12]}.sock")
+        self._srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+        self._srv.bind(self._path)
+        self._srv.listen(8)
+        self._srv.settimeout(0.2)
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._serve, daemon=True)
+        self._thread.start()
+
+    def _serve(self) -> None:
+        import socket
+
+        while not self._stop.is_set():
+            try:
+                conn, _ = self._srv.accept()
+            except (TimeoutError, OSError):
+                continue
+            with conn:
+                try:
+                    socket.send_fds(conn, [b"fd"], [self.arena.fd])
+                    conn.settimeout(5.0)
+                    conn.recv(1)  # the agent confirms it holds its duplicate
+                except OSError:
+                    pass
+
+    def empty(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        n = dtype.itemsize
+        for s in shape:
+            n *= int(s)
+        off = self._cursor
+        if off + n > self.arena.size:
+            raise MemoryError(f"replicated arena of {self.arena.size} bytes is full ({off} used, {n} requested): "
+                              "create the client with a larger replicated_arena_bytes")
+        self._cursor = (off + n + 255) // 256 * 256
+        return self.arena.tensor(off, tuple(shape), dtype)
+
+    def contains(self, t: torch.Tensor) -> bool:
+        return t.is_cuda and self.arena.va <= t.data_ptr() < self.arena.va + self.arena.size
+
+    def ticket(self) -> dict:
+        return {"socket": self._path, "size": self.arena.size, "pid": os.getpid(), "device_index": self.arena.device.index,
+                "va": self.arena.va}
+
+    def close(self) -> None:
+        self._stop.set()
+        self._thread.join(timeout=1.0)
+        self._srv.close()
+        try:
+            os.unlink(self._path)
+        except OSError:
+            pass
+        self.arena.close()
 
 
 class BatchHandler:
@@ -143,8 +225,11 @@ class TensorBusClient:
         lmdb_command_queue_path: str | None = None,
         agent_state_lmdb_path: str | None = None,
         connection_timeout: float = 30.0,
+        replicated_arena_bytes: int | None = None,
     ):
         self.agent_rank = agent_rank
+        self.replicated_arena_bytes = replicated_arena_bytes or int(os.environ.get("TENSOR_BUS_REPLICATED_ARENA_BYTES", 256 << 20))
+        self._arena: ReplicatedArena | None = None
         if agent_state_lmdb_path is None:
             agent_state_lmdb_path = os.environ.get("TENSOR_BUS_STATE_PATH")
         if agent_state_lmdb_path is None:
@@ -242,7 +327,7 @@ class TensorBusClient:
             from ..parallel.peer import PeerMemory
 
             self._peer = PeerMemory(next(t.device for t, _ in tensors if t.is_cuda))
-        payload = [(pair, memoryview(encode_tensor(t, self._peer))) for t, pair in tensors]
+        payload = [(pair, memoryview(encode_tensor(t, self._peer, self._arena))) for t, pair in tensors]
         # the registered tensors must outlive the registration: kept until the batch handler is closed
         self._keepalive.setdefault(batch_id, []).extend(t for t, _ in tensors)
         msg = RegisterTensors(batch_id=batch_id, tensors=payload, bucket_size=bucket_size)
@@ -251,6 +336,15 @@ class TensorBusClient:
         handler = BatchHandler(self, batch_id, list(dict.fromkeys(pair for _, pair in tensors)))
         handler._pending = None if blocking else done
         return handler
+
+    def empty_replicated(self, shape, dtype: torch.dtype, device=None) -> torch.Tensor:
+        """An uninitialised CUDA tensor in this client's replicated arena: register it as a `Replicate` target and
+        producers write every replica with one NVLS multicast store instead of one store per replica.  (Tensors
+        allocated any other way still work: their fan-out is one peer store per replica.)"""
+        if self._arena is None:
+            dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+            self._arena = ReplicatedArena(self.replicated_arena_bytes, dev)
+        return self._arena.empty(shape, dtype)
 
     def transfer(self, batch_id: str, transfer_type: Literal["send", "recv"], blocking: bool = False, timeout: float = 30.0):
         msg = Transfer(batch_id=batch_id, transfer_type=transfer_type)
@@ -271,6 +365,10 @@ class TensorBusClient:
 
     def close(self) -> None:
         self._keepalive.clear()
+        if self._arena is not None:
+            # the agent keeps its own handle on the memory: closing here only ends this process's mapping
+            self._arena.close()
+            self._arena = None
         self.command_queue.close(destroy=False)
         if self.state is not None:
             self.state.close()
