@@ -4,6 +4,10 @@
 
     python examples/weight_sync/launch.py --side-size 4 --model llama3-8b --syncs 5      # 8 GPUs
     python examples/weight_sync/launch.py --side-size 2 --model tiny --device cpu        # no GPU: gloo data path
+    python examples/weight_sync/launch.py --scenario moe --trainer-mesh 2x2 --inference-mesh 2x2 --device cpu
+
+`--scenario moe` runs `moe_worker.py`: a 2-D HSDP trainer mesh plus a 3-D expert mesh, eight named pairs, fused
+qkv / gate-up tensors registered as views, and rounds gated on control keys (see that file).
 
 Same process layout as the reference's launcher (examples/vllm_weight_sync/launch.py:113-143): agents first, then the
 two worker groups with `AGENT_RANK_OFFSET` 0 and n.  Exit status 0 iff every inference rank verified its shards.
@@ -38,9 +42,18 @@ def main() -> int:
     ap.add_argument("--source-dtype", default="bfloat16")
     ap.add_argument("--share-gpu", action="store_true", help="run every agent and worker on GPU 0 (several ranks per GPU)")
     ap.add_argument("--timeout", type=float, default=600.0)
+    ap.add_argument("--scenario", default="dense", choices=["dense", "moe"])
+    ap.add_argument("--trainer-mesh", default="2x2", help="moe scenario: dp_replicate x dp_shard of the trainer side")
+    ap.add_argument("--inference-mesh", default="2x2", help="moe scenario: dp x tp of the inference side")
     args = ap.parse_args()
     n = args.side_size
     world = 2 * n
+    sides = [("trainer", 0, n), ("inference", n, n)]
+    if args.scenario == "moe":
+        nt = int(args.trainer_mesh.split("x")[0]) * int(args.trainer_mesh.split("x")[1])
+        ni = int(args.inference_mesh.split("x")[0]) * int(args.inference_mesh.split("x")[1])
+        world = nt + ni
+        sides = [("trainer", 0, nt), ("inference", nt, ni)]
     prefix = os.path.join(tempfile.mkdtemp(prefix="etha_bus_"), "agent_rank")
     master_port, store_port = free_port(), free_port()
     base = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), MASTER_ADDR="127.0.0.1")
@@ -56,13 +69,19 @@ def main() -> int:
         if args.device == "cpu":
             argv += ["--device", "cpu"]
         spawn(f"agent{r}", argv, env)
-    for role, offset in (("trainer", 0), ("inference", n)):
-        for r in range(n):
-            env = dict(base, RANK=str(r), WORLD_SIZE=str(n), LOCAL_RANK=str(r + offset if args.device == "cuda" and not args.share_gpu else 0),
+    for role, offset, size in sides:
+        for r in range(size):
+            env = dict(base, RANK=str(r), WORLD_SIZE=str(size), LOCAL_RANK=str(r + offset if args.device == "cuda" and not args.share_gpu else 0),
                        AGENT_RANK_OFFSET=str(offset))
-            spawn(f"{role}{r}", [os.path.join(HERE, "worker.py"), "--role", role, "--model", args.model, "--side-size", str(n),
-                                 "--syncs", str(args.syncs), "--path-prefix", prefix, "--device", args.device,
-                                 "--source-dtype", args.source_dtype], env)
+            if args.scenario == "moe":
+                argv = [os.path.join(HERE, "moe_worker.py"), "--role", role, "--trainer-mesh", args.trainer_mesh,
+                        "--inference-mesh", args.inference_mesh, "--rounds", str(args.syncs), "--path-prefix", prefix,
+                        "--store-port", str(store_port), "--device", args.device]
+            else:
+                argv = [os.path.join(HERE, "worker.py"), "--role", role, "--model", args.model, "--side-size", str(n),
+                        "--syncs", str(args.syncs), "--path-prefix", prefix, "--device", args.device,
+                        "--source-dtype", args.source_dtype]
+            spawn(f"{role}{r}", argv, env)
     deadline = time.time() + args.timeout
     workers = [(t, p) for t, p in procs if not t.startswith("agent")]
     status = 0

@@ -26,16 +26,47 @@ def test_example_cpu_two_plus_two():
     assert out.count('"golden_match": true') == 4
 
 
-@pytest.mark.gpu
-@pytest.mark.multigpu
-@pytest.mark.timeout(900)
-def test_example_gpu_peer_to_peer():
+def _side_for_gpus() -> int:
     import torch
 
-    # 1+1 GPUs by default; ETHA_TEST_LARGE=1 runs 2+2 when four GPUs are present
-    side = 2 if (torch.cuda.device_count() >= 4 and os.environ.get("ETHA_TEST_LARGE") == "1") else 1
-    out = _run("--side-size", str(side), "--model", "tiny", "--syncs", "3", "--source-dtype", "float32")
+    n = torch.cuda.device_count()
+    return 4 if n >= 8 else (2 if n >= 4 else 1)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.timeout(1800)
+@pytest.mark.parametrize("source_dtype", ["float32", "bfloat16"])
+def test_example_gpu_peer_to_peer(source_dtype):
+    """The reference's integration test (Qwen3-0.6B shapes, 10 transfers, fp32 -> bf16 and same-dtype, one trainer
+    group and one inference group behind agents; tests/test_distributed_model_transfer.py:59-157) at the largest
+    scale the machine allows: 4+4 GPUs on eight, 2+2 on four, 1+1 (tiny model) on two."""
+    side = _side_for_gpus()
+    model, syncs = ("qwen3-0.6b", 10) if side >= 2 else ("tiny", 3)
+    out = _run("--side-size", str(side), "--model", model, "--syncs", str(syncs), "--source-dtype", source_dtype, timeout=1500)
     assert out.count('"golden_match": true') == 2 * side
+
+
+@pytest.mark.timeout(900)
+def test_moe_example_cpu_hsdp_and_expert_meshes():
+    """2-D HSDP trainer mesh + 3-D expert mesh -> 2-D TP / 1-D EP consumers, eight named pairs, fused qkv and gate-up
+    tensors registered as views on both sides (guard rows checked), rounds gated on control keys."""
+    out = _run("--scenario", "moe", "--trainer-mesh", "2x2", "--inference-mesh", "2x2", "--device", "cpu", "--syncs", "2")
+    assert out.count('"golden_match": true') == 8 and out.count('"pairs": 8') == 8
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.timeout(1800)
+def test_moe_example_gpu():
+    import torch
+
+    n = torch.cuda.device_count()
+    if n < 4:
+        pytest.skip("the MoE example needs at least 2+2 GPUs")
+    mesh = "2x2" if n >= 8 else "1x2"
+    out = _run("--scenario", "moe", "--trainer-mesh", mesh, "--inference-mesh", mesh, "--syncs", "3", timeout=1500)
+    assert out.count('"golden_match": true') == (8 if n >= 8 else 4)
 
 
 @pytest.mark.gpu

@@ -17,8 +17,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 def test_bucket_comm_over_nccl():
     import torch
 
-    # 1+1 GPUs by default; ETHA_TEST_LARGE=1 runs 2+2 (adds Shard(0)->Shard(1) and a Partial source) on four GPUs
-    n = 4 if (torch.cuda.device_count() >= 4 and os.environ.get("ETHA_TEST_LARGE") == "1") else 2
+    # 1+1 GPUs, or 2+2 when four are present (adds Shard(0)->Shard(1), a BROADCAST to two replicas and a Partial source)
+    n = 4 if torch.cuda.device_count() >= 4 else 2
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(n), "--master-addr", "127.0.0.1",
            "--master-port", str(free_port()), os.path.join(HERE, "nccl_bucket_worker.py")]
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=400)
