@@ -1,5 +1,9 @@
 """A tiny in-process etcd v3 JSON gateway (put / range / deleterange) for tests and for boxes with no
-etcd binary.  Not a consensus store: one process, one dict, enough to exercise `EtcdStore`."""
+etcd binary.  Not a consensus store: one process, one dict, enough to exercise `EtcdStore`.
+
+Answers are shaped like the real gateway's proto3 JSON: 64-bit integers are strings (`"count": "3"`,
+`"deleted": "1"`, `"revision": "17"`) and fields holding a default value are left out altogether (no `kvs` for an
+empty range, no `value` for an empty value, no `deleted` when nothing was deleted)."""
 
 from __future__ import annotations
 
@@ -13,6 +17,7 @@ class FakeEtcdGateway:
     def __init__(self, host: str = "127.0.0.1", port: int = 0):
         self._data: dict[bytes, bytes] = {}
         self._lock = threading.Lock()
+        self._revision = 1
         outer = self
 
         class Handler(BaseHTTPRequestHandler):
@@ -45,21 +50,30 @@ class FakeEtcdGateway:
 
     def _handle(self, op: str, body: dict) -> dict:
         with self._lock:
+            header = {"header": {"cluster_id": "1", "member_id": "1", "revision": str(self._revision), "raft_term": "2"}}
             if op == "put":
+                self._revision += 1
                 self._data[base64.b64decode(body["key"])] = base64.b64decode(body.get("value", ""))
-                return {"header": {}}
+                return header
             if op == "range":
                 keys = self._select(body)
                 limit = int(body.get("limit", 0))
                 if limit:
                     keys = keys[:limit]
                 enc = lambda b: base64.b64encode(b).decode("ascii")
-                return {"kvs": [{"key": enc(k), "value": enc(self._data[k])} for k in keys], "count": str(len(keys))}
+                out = dict(header)
+                if keys:
+                    out["kvs"] = [dict({"key": enc(k), "mod_revision": str(self._revision)},
+                                       **({"value": enc(self._data[k])} if self._data[k] else {})) for k in keys]
+                    out["count"] = str(len(keys))
+                return out
             if op == "deleterange":
                 keys = self._select(body)
                 for k in keys:
                     del self._data[k]
-                return {"deleted": str(len(keys))}
+                if keys:
+                    self._revision += 1
+                return dict(header, **({"deleted": str(len(keys))} if keys else {}))
         return {"error": f"unknown op {op}"}
 
     def start(self) -> "FakeEtcdGateway":

@@ -154,3 +154,27 @@ def test_barrier_helpers(store):
     assert store.barrier_count("b/go:1", ranks) == 0
     # counters
     assert store.counter_add("b/gen") == 1 and store.counter_add("b/gen") == 2 and store.counter_add("b/gen", 0) == 2
+
+
+def test_etcd_client_accepts_proto3_json_shapes():
+    """The gateway writes int64 fields as strings and leaves out fields with default values: no `kvs` for an empty
+    range, no `value` for an empty value, no `deleted` when nothing matched."""
+    gw = FakeEtcdGateway().start()
+    try:
+        s = EtcdStore(gw.host, gw.port, namespace="p3")
+        assert s.get("missing") is None and s.exists("missing") is False
+        assert s.delete("missing") is False
+        s.set("empty", "")
+        assert s.get("empty") == b"" and s.exists("empty") is True
+        assert s.try_get("empty") is None
+        s.set_bytes("bin", b"\x00\x01")
+        s.set("pair:x/rank:0/a", "1")
+        s.set("pair:x/rank:1/a", "1")
+        assert s.poll_keys("pair:x/rank:*/a") == ["pair:x/rank:0/a", "pair:x/rank:1/a"]
+        assert s.poll_keys("pair:y/rank:*/a") == []
+        assert s.delete("bin") is True and s.get_bytes("bin") is None
+        assert s.counter_add("n") == 1 and s.counter_add("n", 2) == 3
+        s.close(cleanup=True)
+        assert EtcdStore(gw.host, gw.port, namespace="p3").get("empty") is None
+    finally:
+        gw.stop()
