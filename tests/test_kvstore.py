@@ -178,3 +178,42 @@ def test_etcd_client_accepts_proto3_json_shapes():
         assert EtcdStore(gw.host, gw.port, namespace="p3").get("empty") is None
     finally:
         gw.stop()
+
+
+def test_etcd_waits_sleep_on_a_watch_stream():
+    """Blocking waits open a watch, check once, and then issue no request until an event arrives."""
+    import threading
+    import time
+
+    gw = FakeEtcdGateway().start()
+    try:
+        s = EtcdStore(gw.host, gw.port, namespace="w")
+        writer = EtcdStore(gw.host, gw.port, namespace="w")
+        calls = {"range": 0}
+        real = s._call
+
+        def counting(op, body):
+            calls[op] = calls.get(op, 0) + 1
+            return real(op, body)
+
+        s._call = counting
+        threading.Timer(0.4, lambda: writer.set("late", "v")).start()
+        t0 = time.monotonic()
+        assert s.wait_for_key("late", timeout=5.0) == b"v"
+        assert 0.3 < time.monotonic() - t0 < 3.0
+        assert calls["range"] <= 3, f"{calls['range']} range requests: the wait polled instead of watching"
+        # several keys under a prefix, arriving one by one
+        calls["range"] = 0
+        for i, delay in enumerate((0.1, 0.2, 0.3)):
+            threading.Timer(delay, lambda i=i: writer.set(f"pair:p/rank:{i}/t", "1")).start()
+        got = s.wait_for_keys("pair:p/rank:*/t", 3, timeout=5.0)
+        assert got == [f"pair:p/rank:{i}/t" for i in range(3)] and calls["range"] <= 6
+        threading.Timer(0.2, lambda: writer.set("state", "ready")).start()
+        writer.set("state", "starting")
+        assert s.wait_for_value("state", "ready", timeout=5.0) == b"ready"
+        with pytest.raises(TimeoutError):
+            s.wait_for_key("never", timeout=0.3)
+        with pytest.raises(TimeoutError):
+            s.wait_for_keys("pair:q/rank:*/t", 1, timeout=0.3)
+    finally:
+        gw.stop()
