@@ -292,9 +292,12 @@ class P2PBatch:
                 full = tuple(slice(0, n) for n in s_shapes[s])
                 out.append((s, full, s_shapes[s], [(t, full)]))
             return [], out
-        m2m = layout.plan()
+        from .planner import is_strided_shard
+
+        strided = any(is_strided_shard(p) for p in tuple(layout.source_placements) + tuple(layout.target_placements))
+        m2m = None if strided else layout.plan()  # a strided shard has explicit boxes only
         out = []
-        even = layout.global_shape is None
+        even = layout.global_shape is None and not strided
         if even:
             try:
                 for route in m2m.routes:

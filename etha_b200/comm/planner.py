@@ -37,12 +37,45 @@ def mesh_tensor_of(mesh: Any) -> torch.Tensor:
     return t.reshape(1) if t.dim() == 0 else t
 
 
-def _check_placements(placements: Sequence[Placement], mesh: torch.Tensor, side: str) -> None:
+try:  # a private DTensor placement; since torch 2.11 it is no longer a subclass of Shard
+    from torch.distributed.tensor.placement_types import _StridedShard
+except ImportError:  # pragma: no cover
+    _StridedShard = ()
+
+
+def is_strided_shard(p: Placement) -> bool:
+    return bool(_StridedShard) and isinstance(p, _StridedShard)
+
+
+def shards_dim(p: Placement) -> int | None:
+    """Tensor dim a placement cuts (`Shard` or `_StridedShard`), else None."""
+    return p.dim if isinstance(p, Shard) or is_strided_shard(p) else None
+
+
+def _check_placements(placements: Sequence[Placement], mesh: torch.Tensor, side: str, allow_strided: bool = False) -> None:
     if len(placements) != mesh.dim():
         raise ValueError(f"{side}: {len(placements)} placements for a {mesh.dim()}-d mesh")
-    for p in placements:
+    for i, p in enumerate(placements):
+        if is_strided_shard(p):
+            if not allow_strided:
+                raise NotImplementedError(
+                    f"{side}: {p!r} has no shape-independent plan; use the explicit-box planner "
+                    "(etha_b200.comm.shaped.plan_for_shape, or a PairLayout in a P2PBatch, which selects it itself)")
+            # `_StridedShard(d, split_factor=f)` on mesh dim i says: dim d was cut FIRST by later mesh dims of total
+            # size f (e.g. tensor parallel), and only then by mesh dim i (e.g. FSDP).  The local shard is one
+            # contiguous box exactly when the later mesh dims that shard d multiply to f; other combinations give a
+            # strided union of pieces, which a box plan cannot express.
+            later = 1
+            for size, q in zip(mesh.shape[i + 1:], placements[i + 1:]):
+                if shards_dim(q) == p.dim:
+                    later *= int(size)
+            if later != p.split_factor:
+                raise NotImplementedError(
+                    f"{side}: {p!r} on mesh dim {i} needs later mesh dims sharding dim {p.dim} of total size "
+                    f"{p.split_factor}, found {later}: the local shard would not be a contiguous box")
+            continue
         if not isinstance(p, (Shard, Replicate, Partial)):
-            raise NotImplementedError(f"{side}: placement {p!r} is not supported (Shard, Replicate, Partial only)")
+            raise NotImplementedError(f"{side}: placement {p!r} is not supported (Shard, Replicate, Partial, _StridedShard only)")
 
 
 def tensor_ndim_of(*placement_lists: Sequence[Placement]) -> int:

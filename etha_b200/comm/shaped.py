@@ -8,6 +8,11 @@ case: it computes every rank's box of the global tensor with DTensor's own arith
 consumer boxes with producer boxes.  The result is a list of explicit transfers with the same semantics
 as the lcm plan (same replica-choice rule: consumer number j reads from the family of producer number
 `j mod S`; same Partial families), and for evenly divisible shapes it moves exactly the same bytes.
+
+It is also the planner for `_StridedShard` placements (the FSDP-over-TP layout the reference's CPU test and
+benchmark use as a target, tests/test_communication_cpu.py:43, bench/transfer_benchmark.py:386-390): whenever the
+strided shard is matched by later mesh dims of its split factor, every rank's shard is one box and is planned like
+any other.
 """
 
 from __future__ import annotations
@@ -21,7 +26,7 @@ from torch.distributed.tensor._utils import _compute_local_shape_and_global_offs
 from torch.distributed.tensor.placement_types import Partial, Placement, Replicate, Shard
 
 from .ir import Chunk, PartialFamily, Transport, partial_family
-from .planner import _check_placements, mesh_tensor_of
+from .planner import _check_placements, is_strided_shard, mesh_tensor_of, shards_dim
 
 __all__ = ["ShapedRoute", "ShapedPlan", "plan_for_shape", "shaped_to_chunks", "infer_global_shape", "needs_shaped_plan"]
 
@@ -60,28 +65,28 @@ def needs_shaped_plan(mesh: Any, placements: Sequence[Placement], global_shape: 
     m = mesh_tensor_of(mesh)
     counts: dict[int, int] = {}
     for size, p in zip(m.shape, placements):
-        if isinstance(p, Shard):
+        if shards_dim(p) is not None:
             counts[p.dim] = counts.get(p.dim, 1) * int(size)
-    return any(global_shape[d] % c for d, c in counts.items())
+    return any(is_strided_shard(p) for p in placements) or any(global_shape[d] % c for d, c in counts.items())
 
 
 def plan_for_shape(source_mesh: Any, source_placements: Sequence[Placement], target_mesh: Any,
                    target_placements: Sequence[Placement], global_shape: Sequence[int]) -> ShapedPlan:
     smesh, tmesh = mesh_tensor_of(source_mesh), mesh_tensor_of(target_mesh)
     source_placements, target_placements = tuple(source_placements), tuple(target_placements)
-    _check_placements(source_placements, smesh, "source")
-    _check_placements(target_placements, tmesh, "target")
+    _check_placements(source_placements, smesh, "source", allow_strided=True)
+    _check_placements(target_placements, tmesh, "target", allow_strided=True)
     if any(isinstance(p, Partial) for p in target_placements):
         raise NotImplementedError("Partial is a source-only placement")
     shape = tuple(int(n) for n in global_shape)
     ndim = len(shape)
     for p in list(source_placements) + list(target_placements):
-        if isinstance(p, Shard) and p.dim >= ndim:
+        if shards_dim(p) is not None and p.dim >= ndim:
             raise ValueError(f"{p} on a {ndim}-d tensor")
     reductions = [(i, p.reduce_op) for i, p in enumerate(source_placements) if isinstance(p, Partial)]
     sboxes, tboxes = _boxes(smesh, source_placements, shape), _boxes(tmesh, target_placements, shape)
     s_coords, t_coords = list(sboxes), list(tboxes)
-    shard_dims = [i for i, p in enumerate(source_placements) if isinstance(p, Shard)]
+    shard_dims = [i for i, p in enumerate(source_placements) if shards_dim(p) is not None]
     table: dict[tuple[int, Box], list[tuple[int, Box]]] = {}
     for j, tc in enumerate(t_coords):
         fam = s_coords[j % len(s_coords)]
@@ -115,7 +120,7 @@ def _global_by_brute_force(m: torch.Tensor, placements, local_shapes) -> list[in
     ndim = len(local_shapes[first])
     out = list(local_shapes[first])
     for d in range(ndim):
-        dims = [i for i, p in enumerate(placements) if isinstance(p, Shard) and p.dim == d]
+        dims = [i for i, p in enumerate(placements) if shards_dim(p) == d]
         if not dims:
             continue
         total = 0

@@ -81,6 +81,7 @@ class FakeEtcdGateway:
                 if not send({"result": {"header": {"revision": str(self._revision)}, "events": [ev]}}):
                     return
         finally:
+            handler.close_connection = True
             with self._lock:
                 self._watchers = [w for w in self._watchers if w[1] is not q]
 

@@ -11,7 +11,7 @@ import math
 import numpy as np
 import pytest
 import torch
-from torch.distributed.tensor.placement_types import Replicate, Shard
+from torch.distributed.tensor.placement_types import Replicate, Shard, _StridedShard
 
 from etha_b200.comm.baselines import local_slice_of
 from etha_b200.comm.p2p import P2PBatch, PairLayout
@@ -76,6 +76,7 @@ CASES = [
     ((2,), (Shard(0),), (2,), (Shard(1),), (1000, 333)),
     ((2,), (Shard(0),), (2,), (Shard(1),), (7, 4096)),
     ((2, 2), (Shard(0), Shard(1)), (3,), (Shard(0),), (10, 7)),
+    ((4,), (Shard(0),), (2, 2), (_StridedShard(0, split_factor=2), Shard(0)), (32, 16)),
 ]
 
 

@@ -5,7 +5,7 @@ import math
 import pytest
 import torch
 import torch.distributed as dist
-from torch.distributed.tensor.placement_types import Partial, Replicate, Shard
+from torch.distributed.tensor.placement_types import Partial, Replicate, Shard, _StridedShard
 
 from etha_b200.comm import bucket_comm, chunk_to_bucket_ops, m2m_to_chunks, plan_m2m
 from etha_b200.comm.baselines import local_slice_of
@@ -23,8 +23,15 @@ CASES = [
     ((3,), (Shard(0),), (2, 2), (R, Shard(0)), (5, 6)),
     ((2, 2), (Shard(0), Shard(0)), (4,), (Shard(1),), (9, 9)),
     ((2,), (Partial(),), (2,), (Shard(0),), (5, 3)),
+    # FSDP over TP: the strided shard on mesh dim 0 follows the plain shard on mesh dim 1
+    ((4,), (Shard(0),), (2, 2), (_StridedShard(0, split_factor=2), Shard(0)), (16, 6)),
+    ((2, 2), (_StridedShard(1, split_factor=2), Shard(1)), (3,), (Shard(0),), (9, 8)),
+    # layouts of the reference's CPU test: [R, R, S0, S1] -> [R, _StridedShard(1, 2), R, S1]
+    ((1, 1, 2, 2), (R, R, Shard(0), Shard(1)), (2, 1, 1, 2), (R, _StridedShard(1, split_factor=2), R, Shard(1)), (64, 64)),
+    ((1, 2, 2, 1), (R, R, Shard(0), Shard(1)), (1, 2, 1, 2), (R, _StridedShard(1, split_factor=2), R, Shard(1)), (64, 64)),
     ((4,), (Shard(0),), (4,), (Shard(1),), (64, 64)),  # even: must move exactly what the lcm plan moves
 ]
+N_GLOO = 9  # the cases before the 8-rank ones and the even one run on gloo
 
 
 @pytest.mark.parametrize("case", CASES)
@@ -47,6 +54,8 @@ def test_plan_covers_every_consumer_element_exactly_once(case):
         assert torch.equal(got[r], local_slice_of(full, tmesh, tp, r))
         assert bool((hits[r] == 1).all())
     assert needs_shaped_plan(smesh, sp, shape) or needs_shaped_plan(tmesh, tp, shape) or case is CASES[-1]
+    if case is CASES[-1]:
+        assert not needs_shaped_plan(smesh, sp, shape) and not needs_shaped_plan(tmesh, tp, shape)
     local_shapes = {r: tuple(local_slice_of(full, smesh, eff, r).shape) for r in smesh.reshape(-1).tolist()}
     assert infer_global_shape(smesh, sp, local_shapes) == tuple(shape)
 
@@ -60,7 +69,7 @@ def test_even_shape_moves_same_bytes_as_lcm_plan():
 
 
 def _worker(rank, world):
-    for (ss, sp, ts, tp, shape) in CASES[:7]:
+    for (ss, sp, ts, tp, shape) in CASES[:N_GLOO]:
         ns, nt = math.prod(ss), math.prod(ts)
         if ns + nt > world:
             continue
@@ -94,3 +103,11 @@ def _worker(rank, world):
 
 def test_uneven_redistribution_on_gloo():
     run_distributed(_worker, 7)
+
+
+def test_strided_shard_that_is_not_a_box_is_refused():
+    smesh, tmesh = torch.arange(4), torch.arange(4, 8).view(2, 2)
+    with pytest.raises(NotImplementedError, match="contiguous box"):
+        plan_for_shape(smesh, (Shard(0),), tmesh, (_StridedShard(0, split_factor=2), R), (16, 4))
+    with pytest.raises(NotImplementedError, match="explicit-box planner"):
+        plan_m2m(smesh, (Shard(0),), tmesh, (_StridedShard(0, split_factor=2), Shard(0)))
