@@ -51,6 +51,7 @@ typedef CUresult (*MemAddrFreeFn)(CUdeviceptr, size_t);
 typedef CUresult (*McCreateFn)(CUmemGenericAllocationHandle*, const CUmulticastObjectProp*);
 typedef CUresult (*McAddDevFn)(CUmemGenericAllocationHandle, CUdevice);
 typedef CUresult (*McBindFn)(CUmemGenericAllocationHandle, size_t, CUmemGenericAllocationHandle, size_t, size_t, unsigned long long);
+typedef CUresult (*McBindAddrFn)(CUmemGenericAllocationHandle, size_t, CUdeviceptr, size_t, unsigned long long);
 typedef CUresult (*McUnbindFn)(CUmemGenericAllocationHandle, CUdevice, size_t, size_t);
 typedef CUresult (*McGranFn)(size_t*, const CUmulticastObjectProp*, CUmulticastGranularity_flags);
 
@@ -213,6 +214,14 @@ int etha_mc_bind(uint64_t mc_handle, uint64_t offset, uint64_t mem_handle, uint6
   CUresult r = fn_cuMulticastBindMem((CUmemGenericAllocationHandle)mc_handle, offset, (CUmemGenericAllocationHandle)mem_handle,
                                      mem_offset, size, 0);
   return r == CUDA_SUCCESS ? 0 : drv_fail(r, "cuMulticastBindMem");
+}
+
+// Same, naming the memory by the address it is mapped at in this process instead of by its allocation handle:
+// the form to use for an allocation this process imported from another one.
+int etha_mc_bind_addr(uint64_t mc_handle, uint64_t offset, uint64_t va, uint64_t size) {
+  DRV(cuMulticastBindAddr, McBindAddrFn)
+  CUresult r = fn_cuMulticastBindAddr((CUmemGenericAllocationHandle)mc_handle, offset, (CUdeviceptr)va, size, 0);
+  return r == CUDA_SUCCESS ? 0 : drv_fail(r, "cuMulticastBindAddr");
 }
 
 // Map the multicast object on the current device; stores to the returned address range must be multimem.st.

@@ -42,6 +42,7 @@ def _lib():
         lib.etha_mc_import.argtypes = [i32, P(u64)]
         lib.etha_mc_add_device.argtypes = [u64]
         lib.etha_mc_bind.argtypes = [u64, u64, u64, u64, u64]
+        lib.etha_mc_bind_addr.argtypes = [u64, u64, u64, u64]
         lib.etha_mc_map.argtypes = [u64, u64, P(u64)]
         lib.etha_mc_unbind.argtypes = [u64, u64, u64]
         lib.etha_close_fd.argtypes = [i32]
@@ -112,6 +113,7 @@ class ImportedArena:
             h, va = C.c_uint64(), C.c_uint64()
             L.check(_lib().etha_vmm_import(self.fd, self.size, C.byref(h), C.byref(va)), "vmm_import")
         self.handle, self.va = int(h.value), int(va.value)
+        self.imported = True  # bound to a multicast object by address, not by handle
         self._closed = False
         atexit.register(self.close)
 
@@ -167,6 +169,11 @@ def exchange_fds(rank: int, ranks: Sequence[int], fds: Sequence[int], tag: str, 
     return got
 
 
+class TeamUnavailable(RuntimeError):
+    """The multicast team could not be formed (some member could not bind its memory); every member has left it
+    again and the caller should use plain peer stores."""
+
+
 class NvlsTeam:
     """One multicast object over the arenas of `ranks` (one process and one GPU each, same machine).
 
@@ -211,12 +218,27 @@ class NvlsTeam:
                 lib.etha_close_fd(mc_fd)
             L.check(lib.etha_mc_add_device(self.mc_handle), "mc_add_device")
             barrier()  # every device is part of the team before anybody binds
-            L.check(lib.etha_mc_bind(self.mc_handle, 0, arena.handle, 0, arena.size), "mc_bind")
-            barrier()
-            va = C.c_uint64()
-            L.check(lib.etha_mc_map(self.mc_handle, arena.size, C.byref(va)), "mc_map")
-            self.mc_va = int(va.value)
-            barrier()
+            # an arena this process created is bound by its allocation handle; one it imported from another process
+            # (an agent binding its worker's arena) is bound by the address it is mapped at.  Whether binding worked is
+            # agreed on by all members before anybody maps or stores: one failure dissolves the team everywhere.
+            problem = None
+            rc = lib.etha_mc_bind(self.mc_handle, 0, arena.handle, 0, arena.size) if not getattr(arena, "imported", False) else -1
+            if rc != 0:
+                first = L.last_error() if not getattr(arena, "imported", False) else "imported allocation"
+                rc = lib.etha_mc_bind_addr(self.mc_handle, 0, arena.va, arena.size)
+                if rc != 0:
+                    problem = f"rank {rank}: binding to the multicast object failed (by handle: {first}; by address: {L.last_error()})"
+            self._bound = problem is None
+            problems = [p for p in all_gather(problem) if p]
+            if not problems:
+                va = C.c_uint64()
+                rc = lib.etha_mc_map(self.mc_handle, arena.size, C.byref(va))
+                if rc == 0:
+                    self.mc_va = int(va.value)
+                problems = [p for p in all_gather(None if rc == 0 else f"rank {rank}: mapping the multicast object failed: {L.last_error()}") if p]
+            if problems:
+                self.close()
+                raise TeamUnavailable("; ".join(problems))
         # descriptors of views of a peer's arena (`VmmArena.describe`) resolve to the mappings made here
         owners = all_gather((os.getpid(), arena.device.index, arena.va))
         self.owner_va = {r: o[2] for r, o in zip(self.ranks, owners)}
@@ -239,7 +261,8 @@ class NvlsTeam:
             if self.mc_va:
                 lib.etha_vmm_unmap_release(0, self.mc_va, self.arena.size)
             if self.mc_handle:
-                lib.etha_mc_unbind(self.mc_handle, 0, self.arena.size)
+                if getattr(self, "_bound", True):
+                    lib.etha_mc_unbind(self.mc_handle, 0, self.arena.size)
                 lib.etha_vmm_unmap_release(self.mc_handle, 0, 0)
             for h, va in self._imports:
                 lib.etha_vmm_unmap_release(h, va, self.arena.size)

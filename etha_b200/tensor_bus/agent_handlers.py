@@ -180,7 +180,8 @@ class AgentHandlers:
             if tickets:
                 ticket = next(iter(tickets.values()))
                 batch.arena = self._import_worker_arena(ticket)
-                meta["arena"] = {"size": ticket["size"], "key": (ticket["pid"], ticket["device_index"], ticket["va"])}
+                meta["arena"] = {"size": ticket["size"], "key": (ticket["pid"], ticket["device_index"], ticket["va"]),
+                                 "socket": ticket["socket"]}
             meta["gpu"] = str(torch.cuda.get_device_properties(self.device).uuid)
             from ..ops import device_info
 
@@ -379,13 +380,14 @@ class AgentHandlers:
         multicast object must have memory bound).  Any obstacle (no multicast support, arenas of different sizes)
         leaves `batch.team` unset and the fan-out falls back to one peer store per replica."""
         from ..ops import device_info
-        from ..parallel.arena import NvlsTeam, VmmArena
+        from ..parallel.arena import NvlsTeam, TeamUnavailable, VmmArena
 
         sizes = {m["arena"]["size"] for m in metas.values() if m.get("arena")}
         supported = all(m.get("multicast", False) for m in metas.values())
         if len(sizes) != 1 or not supported or not device_info()["multicast"]:
             logger.warning("Agent %s: batch %s: no multicast team (arena sizes %s, multicast supported everywhere: %s)",
                            self.rank, batch.batch_id, sorted(sizes), supported)
+            self._map_peer_arenas(batch, metas, all_ranks)
             return
         size = sizes.pop()
         mine = batch.arena
@@ -394,13 +396,34 @@ class AgentHandlers:
             if mine.size != size:
                 raise ValueError(f"Batch {batch.batch_id}: replicated arenas of {size} bytes are not a multiple of the "
                                  f"multicast granularity on this device ({mine.size} after rounding)")
-        team = NvlsTeam(self.rank, all_ranks, mine, f"{self.namespace}_{batch.batch_id}_{batch.gen}".replace("/", "_"),
-                        self._kv_all_gather(batch, all_ranks))
+        try:
+            team = NvlsTeam(self.rank, all_ranks, mine, f"{self.namespace}_{batch.batch_id}_{batch.gen}".replace("/", "_"),
+                            self._kv_all_gather(batch, all_ranks))
+        except TeamUnavailable as e:
+            # agreed on by every member: nobody is bound any more, the fan-out uses one peer store per replica.  A
+            # producer still has to reach the consumers' arenas: it maps them like any other peer allocation.
+            logger.warning("Agent %s: batch %s: no multicast team: %s", self.rank, batch.batch_id, e)
+            if batch.scratch_arena is not None:
+                batch.scratch_arena.close()
+                batch.scratch_arena = None
+            self._map_peer_arenas(batch, metas, all_ranks)
+            return
         team.replicas = sorted(r for r in all_ranks if metas[r].get("arena"))
         for r in team.replicas:
             if r != self.rank:  # views of a consumer's arena resolve to the mapping the team made of it
                 self._peer.adopt_mapping(tuple(metas[r]["arena"]["key"]), team.peer_va[r])
         batch.team = team
+
+    def _map_peer_arenas(self, batch: BatchState, metas, all_ranks) -> None:
+        """Without a team, views of another agent's worker arena still have to resolve to an address here: fetch the
+        arena's file descriptor from that worker's socket and map it like the own worker's arena."""
+        for r in all_ranks:
+            info = metas[r].get("arena")
+            if r == self.rank or not info:
+                continue
+            pid, device_index, va = info["key"]
+            self._import_worker_arena({"pid": pid, "device_index": device_index, "va": va, "size": info["size"],
+                                       "socket": info["socket"]})
 
     # ---- Transfer -----------------------------------------------------------------------------------
     def _store_barrier(self, key_prefix: str, ranks, round_no: int):

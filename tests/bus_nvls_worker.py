@@ -1,5 +1,5 @@
 """One worker of the NVLS-through-the-bus test: the trainer (agent rank 0) sends, every inference worker (agent
-ranks 1..n) receives Replicate targets that live in its client's replicated arena.  Launched by test_bus_nvls_gpu.py
+ranks 1..n) receives Replicate targets that live in its client's replicated arena.  Launched by test_y_bus_nvls_gpu.py
 next to one agent process per GPU."""
 
 import argparse
