@@ -318,7 +318,7 @@ def run_ours(args) -> dict:
             "roofline": roof_what,
             "frac_of_roofline": round(roof_ms / ms_step, 3),
             "nvls_multicast_ops": multicast_ops,
-            "l2_policy": "inputs larger than L2 (16 GB per sync vs 126 MB)",
+            "l2_policy": f"inputs larger than L2 ({ws.payload_bytes / 1e9:.1f} GB delivered per sync vs 126 MB)",
             "executor": "p2p copy table, " + ("TMA bulk kernel" if bulk else "LD/ST kernel")
                         + (f" + {ws.batch.table.n_dma_copies} DMA-engine copies ({args.engine})" if ws.batch.table.n_dma_copies else ""),
             "dma_copies_per_step_this_rank": ws.batch.table.n_dma_copies,

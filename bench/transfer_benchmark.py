@@ -17,7 +17,8 @@ configs
 
 Every number is device-timed with CUDA events on each rank, the maximum over ranks is reported, inputs exceed L2
 for all but the smallest sizes (the size is printed), and each line carries the fraction of the NVLink roofline:
-bytes the busiest GPU must send or receive / link bandwidth (measured 770 GB/s per direction; nominal 900).
+bytes the busiest GPU must send or receive / link bandwidth: first against the nominal 900 GB/s per direction, then
+against the copy-engine peak recorded by `bench/link_bench.py` in `bench/link_peak.json`.
 """
 
 from __future__ import annotations
@@ -38,7 +39,9 @@ from bench import init_dist, max_over_ranks  # noqa: E402
 from etha_b200.models import ModelSpec, TensorSpec, fsdp_layout, llama3_8b, mixtral_8x7b, qwen2_7b, vllm_tp_layout  # noqa: E402
 from etha_b200.models.sync import WeightSync  # noqa: E402
 
-LINK_MEASURED, LINK_NOMINAL, HBM_COPY = 770e9, 900e9, 6535e9
+LINK_NOMINAL, HBM_COPY = 900e9, 6535e9
+with open(os.path.join(ROOT, "bench", "link_peak.json")) as _f:
+    LINK_MEASURED = json.load(_f)["copy_engine_GBps"] * 1e9  # cudaMemcpyAsync onto a peer mapping, 1 GiB
 _CASE = [0]  # every rank runs the cases in the same order, so the counter names the rendezvous sockets
 
 
