@@ -29,6 +29,20 @@ def pytest_collection_modifyitems(config, items):
         if "multigpu" in item.keywords and n < 2:
             item.add_marker(skip_multi)
 
+    # Order: everything that needs at most one GPU first, then the multi-process multi-GPU integration tests, and the
+    # allocation-free entry point last of all, so that a run that stops at the first failure (-x) has already been
+    # through the kernels' numerics tests when it reaches the long integration runs.
+    late = ["test_nccl_bucket_gpu", "test_nvls_gpu", "test_example_gpu_peer_to_peer", "test_moe_example_gpu", "test_y_bus_nvls_gpu"]
+
+    def rank(item):
+        if "test_zz_" in item.nodeid:
+            return 100
+        if "multigpu" not in item.keywords:
+            return 0
+        return 1 + next((i for i, name in enumerate(late) if name in item.nodeid), len(late))  # shortest runs first
+
+    items.sort(key=rank)
+
 
 def free_port() -> int:
     with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
