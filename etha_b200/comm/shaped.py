@@ -28,7 +28,17 @@ from torch.distributed.tensor.placement_types import Partial, Placement, Replica
 from .ir import Chunk, PartialFamily, Transport, partial_family
 from .planner import _check_placements, is_strided_shard, mesh_tensor_of, shards_dim
 
-__all__ = ["ShapedRoute", "ShapedPlan", "plan_for_shape", "shaped_to_chunks", "infer_global_shape", "needs_shaped_plan"]
+__all__ = ["BOX_PLAN_ONLY", "ShapedRoute", "ShapedPlan", "plan_for_shape", "shaped_to_chunks", "infer_global_shape", "needs_shaped_plan"]
+
+class _BoxPlanOnly:
+    """Stands in for an `M2MMap` where a layout has no shape-independent plan (`_StridedShard`): the pair is valid,
+    its transfers are planned per tensor from explicit boxes."""
+
+    def __repr__(self) -> str:
+        return "BOX_PLAN_ONLY"
+
+
+BOX_PLAN_ONLY = _BoxPlanOnly()
 
 Box = tuple[tuple[int, int], ...]  # per dim (start, stop) in LOCAL coordinates of the owning rank
 

@@ -30,6 +30,7 @@ from torch.distributed.tensor.placement_types import Partial
 
 from ..comm import chunk_to_bucket_ops, m2m_to_chunks
 from ..comm.bucket_exec import bucket_comm
+from ..comm.ir import M2MMap
 from ..comm.planner import plan_m2m
 from .batch_state import BatchState
 from .commands import CleanupBatch, InitPair, QueryStatus, RegisterTensors, Transfer
@@ -120,10 +121,21 @@ class AgentHandlers:
         if local and remote:
             st.local_mesh, st.local_placements = local
             st.remote_mesh, st.remote_placements = remote
+            def plan(smesh, splc, tmesh, tplc):
+                from ..comm.planner import _check_placements, is_strided_shard
+                from ..comm.shaped import BOX_PLAN_ONLY
+
+                if any(is_strided_shard(p) for p in tuple(splc) + tuple(tplc)):
+                    # no shape-independent plan exists for a strided shard: validate now, plan per tensor from boxes
+                    _check_placements(tuple(splc), smesh, "source", allow_strided=True)
+                    _check_placements(tuple(tplc), tmesh, "target", allow_strided=True)
+                    return BOX_PLAN_ONLY
+                return plan_m2m(smesh, splc, tmesh, tplc)
+
             if not any(isinstance(p, Partial) for p in st.remote_placements):
-                st.m2m_send = plan_m2m(st.local_mesh, st.local_placements, st.remote_mesh, st.remote_placements)
+                st.m2m_send = plan(st.local_mesh, st.local_placements, st.remote_mesh, st.remote_placements)
             if not any(isinstance(p, Partial) for p in st.local_placements):
-                st.m2m_recv = plan_m2m(st.remote_mesh, st.remote_placements, st.local_mesh, st.local_placements)
+                st.m2m_recv = plan(st.remote_mesh, st.remote_placements, st.local_mesh, st.local_placements)
         self.pairs[pair] = st
         self.state.set_matched(pair)
         logger.info("Agent %s: pair '%s' matched: %s %s <-> %s %s", self.rank, pair, local_name, local_ranks, remote_name, remote_ranks)
@@ -257,8 +269,9 @@ class AgentHandlers:
         """Chunks of one tensor: the lcm plan when every shard of both sides divides evenly, explicit boxes otherwise
         (decided from all ranks' shapes, so both sides agree)."""
         from ..comm.chunks import plan_fits_shapes
+        from ..comm.shaped import BOX_PLAN_ONLY
 
-        if plan_fits_shapes(m2m, source_shapes, target_shapes):
+        if m2m is not BOX_PLAN_ONLY and plan_fits_shapes(m2m, source_shapes, target_shapes):
             return m2m_to_chunks(m2m, self.rank, source_tensor=source, target_tensor=target, transfer_dtype=wire,
                                  source_mesh=smesh, tensor_id=k)
         from ..comm.shaped import infer_global_shape, plan_for_shape, shaped_to_chunks
@@ -296,7 +309,8 @@ class AgentHandlers:
                     break
                 lay = (PairLayout(ps.local_mesh, ps.local_placements, ps.remote_mesh, ps.remote_placements) if sending
                        else PairLayout(ps.remote_mesh, ps.remote_placements, ps.local_mesh, ps.local_placements))
-                lay._plan = m
+                if isinstance(m, M2MMap):
+                    lay._plan = m  # a layout without a shape-independent plan is planned from boxes by the batch itself
                 layouts.append(lay)
             if not ok:
                 return None

@@ -216,3 +216,32 @@ def test_export_failure_names_the_unsupported_allocators(monkeypatch):
     with pytest.raises(peer_mod.PeerExportError, match="expandable segments") as info:
         pm.describe(FakeTensor())
     assert "VmmArena" in str(info.value) and "invalid argument" in str(info.value)
+
+
+def _strided_worker(rank, world, port, tag, tmp):
+    """FSDP-over-TP target through the bus: 2 trainers hold Shard(0), 4 inference ranks hold
+    (_StridedShard(0, split_factor=2), Shard(0)) on a 2x2 mesh — the placement the reference's CPU test uses."""
+    from torch.distributed.tensor.placement_types import _StridedShard
+
+    agent, th, cq, st = _start_agent(rank, world, port, tag, tmp)
+    client = TensorBusClient(rank, cq, st, connection_timeout=10.0)
+    try:
+        trainer = rank < 2
+        me, other = ("trainer", "inference") if trainer else ("inference", "trainer")
+        mesh = torch.arange(2) if trainer else torch.arange(2, 6).view(2, 2)
+        plc = (Shard(0),) if trainer else (_StridedShard(0, split_factor=2), Shard(0))
+        client.init_pair("w", me, other, 2 if trainer else 4, mesh, plc, timeout=30.0)
+        full = torch.randn(16, 6, generator=torch.Generator().manual_seed(5))
+        mine = local_slice_of(full, mesh, plc, rank).clone()
+        t = mine if trainer else torch.zeros_like(mine)
+        batch = client.register_tensors("strided", [(t, "w")], timeout=30.0)
+        batch.transfer("send" if trainer else "recv", blocking=True, timeout=30.0)
+        if not trainer:
+            assert torch.equal(t, mine)
+        batch.close()
+    finally:
+        _teardown(agent, th, client)
+
+
+def test_strided_shard_target_through_the_bus(tmp_path):
+    run_distributed(_strided_worker, 6, free_port(), "strided", str(tmp_path))
