@@ -109,7 +109,12 @@ def run(args, ref_dir: str) -> dict:
     model = model_of(args.model)
     smesh_t, tmesh_t, s_rule, t_rule, par, _ = layout_for(args, world)
     is_src, is_dst = rank in smesh_t.reshape(-1).tolist(), rank in tmesh_t.reshape(-1).tolist()
-    dtype = torch.bfloat16
+    dtype = torch.bfloat16  # what the consumers hold
+    src_dtype = getattr(torch, getattr(args, "source_dtype", "bfloat16"))  # what the trainer holds
+    if src_dtype != dtype and world == 1:
+        # the reference's single-rank LOCAL chunk reads and writes one tensor, so it cannot convert
+        dist.destroy_process_group()
+        return {"impl": "reference", "unavailable": "the reference's single-rank LOCAL path keeps source and target in one tensor: no dtype conversion"}
     seed = 2
 
     def partial_div(plc):
@@ -123,7 +128,7 @@ def run(args, ref_dir: str) -> dict:
         # a Partial("sum") source holds value / group size on every contributor (exact for powers of two)
         full = full_tensor_for(spec, k, seed, torch.float32, dev) / partial_div(plc)
         shape, off = local_shape_and_offset(spec.shape, mesh_t, plc, rank)
-        out = full[tuple(slice(o, o + n) for o, n in zip(off, shape))].to(dtype).contiguous()
+        out = full[tuple(slice(o, o + n) for o, n in zip(off, shape))].to(src_dtype).contiguous()
         del full
         return out
 
@@ -160,7 +165,9 @@ def run(args, ref_dir: str) -> dict:
                 shape, _ = local_shape_and_offset(spec.shape, tmesh_t, tp, rank)
                 tgt = torch.zeros(shape, dtype=dtype, device=dev)
                 targets.append((k, spec, sp, tp, tgt))
-            chunks += m2m_to_chunks(maps[(sp, tp)], rank=rank, source_tensor=src, target_tensor=tgt,
+            # the wire dtype is the narrower of the two sides, as the reference's agent picks it (agent.py:635-644)
+            wire = None if src_dtype == dtype else (src_dtype if src_dtype.itemsize <= dtype.itemsize else dtype)
+            chunks += m2m_to_chunks(maps[(sp, tp)], rank=rank, source_tensor=src, target_tensor=tgt, transfer_dtype=wire,
                                     source_partial_groups=groups[(sp, tp)] if is_src else None)
             copies = 1
             for size, p in zip(tmesh_t.shape, tp):
@@ -197,7 +204,8 @@ def run(args, ref_dir: str) -> dict:
         for k, spec, sp, tp, tgt in targets:
             div = partial_div(sp)
             full = full_tensor_for(spec, k, seed, torch.float32, dev) * scale[0]
-            full = ((full / div).to(dtype).to(torch.float32) * div).to(dtype) if div > 1 else full.to(dtype)
+            full = ((full / div).to(src_dtype).to(torch.float32) * div).to(src_dtype) if div > 1 else full.to(src_dtype)
+            full = full.to(dtype)
             shape, off = local_shape_and_offset(spec.shape, tmesh_t, tp, rank)
             if not torch.equal(tgt, full[tuple(slice(o, o + n) for o, n in zip(off, shape))]):
                 n_bad += 1
@@ -259,6 +267,7 @@ def run(args, ref_dir: str) -> dict:
             "model": args.model,
             "parallelism": par,
             "layout": args.layout,
+            "source_dtype": getattr(args, "source_dtype", "bfloat16"),
             "tensors": len(model.tensors),
             "payload_bytes": payload,
             "executor": "reference etha.comm.bucket_comm over NCCL" if world > 1 else "reference LOCAL chunks (hand-built), bucket_comm",
