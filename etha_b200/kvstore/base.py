@@ -131,11 +131,20 @@ class KVStore(ABC):
                 count += 1
         return count
 
-    def barrier_arrive(self, key_prefix: str, rank: int, round_no: int = 1, *, component: str | None = None) -> None:
+    def barrier_arrive(self, key_prefix: str, rank: int, round_no: int = 1, n_ranks: int | None = None, *,
+                       component: str | None = None) -> None:
         """Announce `rank` at round `round_no` (1, 2, ...) of the barrier named `key_prefix`.  The same keys are
         reused by every round, so a barrier that runs once per transfer leaves a fixed number of keys behind.
-        Every round must be asked about with the same full list of participants."""
+        Every round must be asked about with the same full list of participants (`n_ranks` of them, for backends
+        that want to recognise the last arrival)."""
         self.mark_reached(key_prefix, rank, round_no, component=component)
+
+    def barrier_wait(self, key_prefix: str, ranks: list[int], round_no: int = 1, timeout_s: float = 0.0, *,
+                     component: str | None = None) -> bool:
+        """True once every rank of `ranks` has arrived at round `round_no`.  `timeout_s` is how long a backend may
+        sleep on a server-side notification; the generic form polls once and returns.  (TCPStore's own `wait` is not
+        used for this: a wait that times out costs milliseconds and leaves its answer pending on the connection.)"""
+        return self.barrier_count(key_prefix, ranks, round_no, component=component) >= len(ranks)
 
     def barrier_count(self, key_prefix: str, ranks: list[int], round_no: int = 1, *, component: str | None = None) -> int:
         """How many of `ranks` have reached round `round_no` (one poll, no waiting)."""

@@ -108,7 +108,8 @@ class TorchTCPStore(KVStore):
     def counter_add(self, key: str, amount: int = 1, *, component: str | None = None) -> int:
         return int(self._store.add(self._prefixed(key, component), amount))
 
-    def barrier_arrive(self, key_prefix: str, rank: int, round_no: int = 1, *, component: str | None = None) -> None:  # noqa: ARG002
+    def barrier_arrive(self, key_prefix: str, rank: int, round_no: int = 1, n_ranks: int | None = None, *,
+                       component: str | None = None) -> None:  # noqa: ARG002
         self._store.add(self._prefixed(f"{key_prefix}/count", component), 1)
 
     def barrier_count(self, key_prefix: str, ranks: list[int], round_no: int = 1, *, component: str | None = None) -> int:
@@ -116,9 +117,8 @@ class TorchTCPStore(KVStore):
         return max(0, min(done, len(ranks)))
 
     def barrier_forget(self, key_prefix: str, rank: int, *, component: str | None = None) -> None:  # noqa: ARG002
-        k = self._prefixed(f"{key_prefix}/count", component)
         try:
-            self._store.delete_key(k)
+            self._store.delete_key(self._prefixed(f"{key_prefix}/count", component))
         except Exception:  # a c10d store without delete: one counter per barrier name is left behind
             pass
 

@@ -44,6 +44,7 @@ from .state_store import StateStore
 logger = logging.getLogger(__name__)
 
 TIME_INTERVAL = 0.001  # command-loop tick
+HOT_JOB_S = 0.05  # a job younger than this is polled without sleeping (a transfer is a few store round trips + the copy)
 HEARTBEAT_PERIOD = 0.2
 ERROR_TTL_S = 120.0  # a failed command's message is kept this long for its client to read, then deleted
 
@@ -141,7 +142,12 @@ class TensorBusAgent(AgentHandlers):
         while not self._stop.is_set():
             # idle: block on the queue semaphore for a tick; with jobs in flight poll fast, a transfer's barrier and
             # completion are a handful of store round trips and should not pay a millisecond sleep each
-            busy = self.step(block_s=TIME_INTERVAL if not self._jobs else 0.00005)
+            if not self._jobs:
+                tick = TIME_INTERVAL
+            else:  # a sleep costs at least 60-100 us of timer slack: too much between the polls of a 5 ms transfer
+                now = time.monotonic()
+                tick = 0.0 if any(now - j.started < HOT_JOB_S for j in self._jobs) else 0.00005
+            busy = self.step(block_s=tick)
             if busy:
                 last = time.monotonic()
             elif max_idle_s is not None and time.monotonic() - last > max_idle_s:
@@ -157,7 +163,8 @@ class TensorBusAgent(AgentHandlers):
 
     def step(self, block_s: float = 0.0) -> bool:
         """One tick: maybe start the next command, advance every running job. Returns True if anything is in flight."""
-        nxt = self.command_queue.peek() if self._jobs else None
+        # another command can only start next to running ones if all of them are handshakes: do not look otherwise
+        nxt = self.command_queue.peek() if (self._jobs and all(j.concurrent for j in self._jobs)) else None
         if not self._jobs or (nxt is not None and self._can_start(isinstance(nxt, InitPair))):
             msg = self.command_queue.dequeue(block=not self._jobs, timeout=block_s)
             if msg is not None:

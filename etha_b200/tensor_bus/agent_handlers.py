@@ -175,7 +175,7 @@ class AgentHandlers:
         batch.key = f"batch:{batch_id}/gen:{batch.gen}"
 
         # publish what the other agents need, then wait for theirs
-        meta = {"rank": self.rank, "kind": kind, "local_name": first.local_name, "gen": batch.gen}
+        meta = {"rank": self.rank, "kind": kind, "local_name": first.local_name, "gen": batch.gen, "host": _hostname()}
         if kind == "cuda":
             from ..parallel.peer import PeerMemory
 
@@ -216,6 +216,11 @@ class AgentHandlers:
                 raise ValueError(f"Batch {batch_id}: rank {r} registered {len(m['descs'])} {m['kind']} tensors, "
                                  f"rank {self.rank} registered {len(entries)} {kind} tensors")
         batch.kind = kind
+        if len({m.get("host") for m in metas.values()}) == 1 and len(all_ranks) > 1:
+            # every agent of the batch runs on this machine: the per-transfer rendezvous uses semaphores, not the store
+            from .node_barrier import NodeBarrier
+
+            batch.node_barrier = NodeBarrier(f"{self.namespace}/{batch.key}", self.rank, all_ranks)
         if kind == "cuda" and len({m.get("host") for m in metas.values()}) == 1:
             if any(m.get("arena") for m in metas.values()):
                 self._join_multicast_team(batch, metas, all_ranks)
@@ -443,8 +448,8 @@ class AgentHandlers:
     def _store_barrier(self, key_prefix: str, ranks, round_no: int):
         """Round `round_no` of the barrier `key_prefix` over `ranks`; yields until everybody has arrived."""
         ranks = list(ranks)
-        self.store.barrier_arrive(key_prefix, self.rank, round_no)
-        while self.store.barrier_count(key_prefix, ranks, round_no) < len(ranks):
+        self.store.barrier_arrive(key_prefix, self.rank, round_no, len(ranks))
+        while not self.store.barrier_wait(key_prefix, ranks, round_no):
             yield
 
     def _transfer_job(self, msg: Transfer):
@@ -464,23 +469,27 @@ class AgentHandlers:
         batch.epoch += 1
         epoch = batch.epoch
         if sending and self.rank == batch.local_leader:
-            # the epoch of the newest send is what receivers compare with the receives they have completed; the
-            # "1"/"0" key of the reference is kept for observers but is not what `query_transfer_signal` reads,
-            # because a late "0" of receive k can overwrite the "1" of send k+1
+            # the epoch of the newest send is what receivers compare with the receives they have completed
             self.store.set(f"{batch.key}/state:send_epoch", str(epoch), component="global")
-            self.store.set(signal_key, "1", component="global")
         all_ranks = sorted(set(batch.local_ranks) | set(batch.remote_ranks))
         # both sides meet here, like the reference's barrier on the batch group (agent.py:457)
-        yield from self._store_barrier(f"{batch.key}/go", all_ranks, epoch)
+        if batch.node_barrier is not None:
+            batch.node_barrier.arrive()
+            while not batch.node_barrier.passed():
+                yield
+        else:
+            yield from self._store_barrier(f"{batch.key}/go", all_ranks, epoch)
 
         ex = batch.send_exec if sending else batch.recv_exec
+        if sending and self.rank == batch.local_leader and ex in ("bucket", "plain"):
+            self.store.set(signal_key, "1", component="global")  # the peer-to-peer path writes it while its copies run
         t0 = time.perf_counter()
         if ex == "bucket":
             bucket_comm(batch.send_buckets if sending else batch.recv_buckets)
         elif ex == "plain":
             yield from self._plain_transfer(batch, sending)
         else:
-            yield from self._p2p_transfer(batch, ex, sending, epoch)
+            yield from self._p2p_transfer(batch, ex, sending, epoch, signal_key)
         ms = (time.perf_counter() - t0) * 1e3
         self.state.put(f"batch:{batch.batch_id}/state:last_{msg.transfer_type}_ms", f"{ms:.3f}".encode())
         if not sending:
@@ -489,7 +498,7 @@ class AgentHandlers:
                 self.store.set(signal_key, "0", component="global")
         logger.info("Agent %s: batch %s %s done in %.2f ms", self.rank, batch.batch_id, msg.transfer_type, ms)
 
-    def _p2p_transfer(self, batch: BatchState, ex, sending: bool, epoch: int):
+    def _p2p_transfer(self, batch: BatchState, ex, sending: bool, epoch: int, signal_key: str | None = None):
         """Producers launch their copy table; every rank whose memory other ranks write (consumers) or read (Partial
         contributors) then waits until those ranks are done — on the device with the bounded flag wait, or through
         the KV store when another agent of the batch drives the same physical GPU."""
@@ -509,6 +518,11 @@ class AgentHandlers:
             if waits_on_device:
                 ex.recv(stream, timeout_s=min(self.store_timeout, 60.0))
         e1.record(stream)
+        if sending and signal_key and self.rank == batch.local_leader:
+            # the reference's "1"/"0" key, kept for observers (`query_transfer_signal` reads the epoch instead, because a
+            # late "0" of receive k can overwrite the "1" of send k+1); written while the copies run, off the critical path
+            self.store.set(signal_key, "1", component="global")
+            signal_key = None
         while not e1.query():
             yield
         ex.check()
@@ -568,6 +582,9 @@ class AgentHandlers:
                 ex.close()
         batch.send_exec = batch.recv_exec = None
         batch.send_buckets = batch.recv_buckets = None
+        if batch.node_barrier is not None:
+            batch.node_barrier.close()
+            batch.node_barrier = None
         if batch.team is not None:  # leave the multicast team (unmap, unbind) before any arena goes away
             batch.team.close()
             batch.team = None

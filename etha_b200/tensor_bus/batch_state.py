@@ -30,6 +30,7 @@ class BatchState:
     flags: Any = None  # CUDA: {"fwd": int32[ranks], "bwd": ...} completion flags other agents write into
     shared_gpu: bool = False  # another agent of the batch drives the same physical GPU: completion goes through the store
     wrote_done: bool = False
+    node_barrier: Any = None  # semaphore rendezvous when every agent of the batch is on this machine
     # NVLS: this agent's arena in the batch's multicast team (the worker's replicated arena, or scratch), the team
     arena: Any = None
     scratch_arena: Any = None

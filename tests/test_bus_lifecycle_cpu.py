@@ -92,6 +92,10 @@ def _cycle_worker(rank, world, port, tag, tmp):
         assert late[0] is None or late[0] <= early[0], f"store keys grew: {early[0]} -> {late[0]}"
         assert late[1] <= early[1], f"state-store slots grew: {early[1]} -> {late[1]}"
         assert late[2] == 0
+        dist.barrier()
+        import os
+
+        assert not [f for f in os.listdir("/dev/shm") if "etha_nb_" in f], "rendezvous semaphores were left behind"
     finally:
         _teardown(agent, th, client)
 
