@@ -342,6 +342,8 @@ class AgentHandlers:
         # two processes time-slicing one GPU must never have one kernel spin on a flag the other one sets
         mine = metas[self.rank]["gpu"]
         batch.shared_gpu = sum(1 for r in all_ranks if metas[r]["gpu"] == mine) > 1
+        gpus = [metas[r]["gpu"] for r in all_ranks]
+        batch.any_shared_gpu = len(set(gpus)) < len(gpus)  # some agent of the batch completes through the store
 
     # ---- NVLS: replicated arenas of the workers bound to one multicast object --------------------------------
     def _import_worker_arena(self, ticket: dict):
@@ -528,9 +530,11 @@ class AgentHandlers:
         ex.check()
         if sending:
             self.state.put(f"batch:{batch.batch_id}/state:last_send_device_ms", f"{e0.elapsed_time(e1):.3f}".encode())
-            # own copies are complete: published (as "done up to this transfer") before any wait
-            self.store.mark_reached(done_prefix, self.rank, epoch)
-            batch.wrote_done = True
+            if batch.any_shared_gpu:
+                # own copies are complete: published (as "done up to this transfer") before any wait, for the agents
+                # that share a GPU with another one and therefore wait on the host
+                self.store.mark_reached(done_prefix, self.rank, epoch)
+                batch.wrote_done = True
         if ex._producers and shared_gpu:
             producers = list(ex._producers)
             while self.store.count_reached(done_prefix, producers, epoch) < len(producers):

@@ -29,6 +29,7 @@ class BatchState:
     kind: str = ""  # "cuda" | "cpu"
     flags: Any = None  # CUDA: {"fwd": int32[ranks], "bwd": ...} completion flags other agents write into
     shared_gpu: bool = False  # another agent of the batch drives the same physical GPU: completion goes through the store
+    any_shared_gpu: bool = False  # some GPU is driven by two agents of the batch: producers publish completion in the store
     wrote_done: bool = False
     node_barrier: Any = None  # semaphore rendezvous when every agent of the batch is on this machine
     # NVLS: this agent's arena in the batch's multicast team (the worker's replicated arena, or scratch), the team
