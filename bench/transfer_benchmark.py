@@ -71,7 +71,7 @@ def run_case(name, model, smesh, tmesh, s_rule, t_rule, args, rank, world, excha
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         from etha_b200.utils.profiling import ProfilingSpec, maybe_enable_profiling
 
-        spec = ProfilingSpec(enable_profiling=bool(args.profile), dump_folder=os.path.join(ROOT, "gpurun_out", "traces"),
+        spec = ProfilingSpec(enable_profiling=bool(args.profile), dump_folder=os.path.join(os.getcwd(), "profiling_traces"),
                              save_traces_folder=name.replace(' ', '_').replace('>', ''),
                              profile_freq=args.steps, warmup_steps=1, active_steps=max(args.steps - 2, 1))
         with maybe_enable_profiling(spec, rank=rank) as prof:
