@@ -228,23 +228,29 @@ class CopyTable:
                 ks.tiles_rest_dev = to_dev(prefix([t for t, _, _ in members[ks.n_bulk_ops:]]))
         return ks
 
+    def _select_dma(self) -> set[int]:
+        """Positions (in `_packed`) of the ops handed to the DMA engines: the largest candidates first, as long as the
+        byte budget `dma_fraction x delivered bytes` is not exceeded (a candidate that does not fit is skipped, smaller
+        ones may still fit).  Their copies are queued in table order, so the producers' rotation is kept."""
+        budget = self.dma_fraction * self.payload_bytes
+        taken: set[int] = set()
+        for nbytes, pos, _copies, _ in sorted(self._dma_candidates, key=lambda c: (-c[0], c[1])):
+            if self.dma_bytes + nbytes > budget:
+                continue
+            taken.add(pos)
+            self.dma_bytes += nbytes
+        for _nbytes, pos, copies, _ in self._dma_candidates:
+            if pos in taken:
+                self._dma += copies
+        return taken
+
     def finalize(self, sm_count: int | None = None) -> "CopyTable":
         if self._final:
             return self
         if sm_count is None:
             sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.sm_count = sm_count
-        # the largest DMA candidates, up to the byte budget, leave the kernels' table
-        budget = self.dma_fraction * self.payload_bytes
-        taken: set[int] = set()
-        for nbytes, pos, copies, _ in sorted(self._dma_candidates, key=lambda c: (-c[0], c[1])):
-            if self.dma_bytes + nbytes > budget:
-                continue
-            taken.add(pos)
-            self.dma_bytes += nbytes
-        for nbytes, pos, copies, _ in self._dma_candidates:  # table order: the producers' rotation is kept
-            if pos in taken:
-                self._dma += copies
+        taken = self._select_dma()
         # two kernel sets share this table: every op (kernels only), and what is left next to the DMA copies
         self._all = self._upload(self._packed)
         self._rest = self._upload([e for i, e in enumerate(self._packed) if i not in taken]) if taken else self._all
