@@ -198,7 +198,6 @@ class AgentHandlers:
             from ..ops import device_info
 
             meta["multicast"] = bool(device_info()["multicast"])
-            meta["host"] = _hostname()
         else:
             meta["descs"] = [(tuple(t.shape), str(t.dtype).replace("torch.", "")) for _, _, t in entries]
         self.store.set_bytes(f"{batch.key}/rank:{self.rank}/meta", pickle.dumps(meta))
@@ -216,6 +215,18 @@ class AgentHandlers:
                 raise ValueError(f"Batch {batch_id}: rank {r} registered {len(m['descs'])} {m['kind']} tensors, "
                                  f"rank {self.rank} registered {len(entries)} {kind} tensors")
         batch.kind = kind
+        try:
+            self._build_executors(batch, entries, metas, all_ranks, kind, flags if kind == "cuda" else None)
+        except Exception:
+            self._drop_batch(batch)  # nothing of a registration that failed half-way stays behind (semaphores, keys, teams)
+            raise
+        self.batches[batch_id] = batch
+        self.state.put(f"batch:{batch_id}/state:multicast_ops", str(batch.multicast_ops).encode())
+        logger.info("Agent %s: batch %s registered (%d tensors, %s)", self.rank, batch_id, len(entries), kind)
+
+    def _build_executors(self, batch: BatchState, entries, metas, all_ranks, kind: str, flags) -> None:
+        """Everything a registration builds once every agent's descriptors are known."""
+        batch_id = batch.batch_id
         if len({m.get("host") for m in metas.values()}) == 1 and len(all_ranks) > 1:
             # every agent of the batch runs on this machine: the per-transfer rendezvous uses semaphores, not the store
             from .node_barrier import NodeBarrier
@@ -234,9 +245,6 @@ class AgentHandlers:
             self._build_buckets(batch, local, metas)
         else:
             self._build_buckets(batch, entries, metas)
-        self.batches[batch_id] = batch
-        self.state.put(f"batch:{batch_id}/state:multicast_ops", str(batch.multicast_ops).encode())
-        logger.info("Agent %s: batch %s registered (%d tensors, %s)", self.rank, batch_id, len(entries), kind)
 
     def _build_buckets(self, batch: BatchState, entries, metas) -> None:
         """CPU tensors: chunks and buckets for both directions (gloo bucket executor)."""
