@@ -476,6 +476,13 @@ class AgentHandlers:
                    "(Partial is only valid as a source placement)" if partial_side else
                    "no executor could be built for that direction when the batch was registered")
             raise RuntimeError(f"Batch {batch.batch_id}: no {msg.transfer_type} plan: {why}.")
+        if batch.in_flight:
+            # an earlier transfer of this batch died between its rendezvous and its completion (a peer that never came,
+            # a timeout): arrivals and epochs of the two sides no longer pair up, so a later rendezvous could let a
+            # producer write before its consumer asked.  Only a fresh registration (a new generation) is safe.
+            raise RuntimeError(f"Batch {batch.batch_id}: an earlier transfer did not complete; close the batch and "
+                               "register it again")
+        batch.in_flight = True
         batch.epoch += 1
         epoch = batch.epoch
         if sending and self.rank == batch.local_leader:
@@ -506,6 +513,7 @@ class AgentHandlers:
             batch.recv_done = epoch
             if self.rank == batch.local_leader:
                 self.store.set(signal_key, "0", component="global")
+        batch.in_flight = False
         logger.info("Agent %s: batch %s %s done in %.2f ms", self.rank, batch.batch_id, msg.transfer_type, ms)
 
     def _p2p_transfer(self, batch: BatchState, ex, sending: bool, epoch: int, signal_key: str | None = None):

@@ -23,6 +23,7 @@ class BatchState:
     recv_buckets: list | None = None
     epoch: int = 0
     recv_done: int = 0  # epoch of the last receive this agent completed
+    in_flight: bool = False  # a transfer has passed its start and not reached its end (stays set if it dies half-way)
     keepalive: list = field(default_factory=list)
     gen: int = 0  # how often this agent has registered this batch id; part of every key of the registration
     key: str = ""  # "batch:{id}/gen:{gen}"

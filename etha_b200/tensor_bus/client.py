@@ -242,6 +242,7 @@ class TensorBusClient:
         self.command_queue = CommandQueue(lmdb_command_queue_path)
         self._peer = None
         self._keepalive: dict[str, list[torch.Tensor]] = {}
+        self._handlers: dict[str, weakref.ref] = {}
 
     # ---- plumbing ------------------------------------------------------------------------------
     def _raise_if_failed(self, sem_name: str, what: str) -> None:
@@ -333,7 +334,14 @@ class TensorBusClient:
         msg = RegisterTensors(batch_id=batch_id, tensors=payload, bucket_size=bucket_size)
         done = self._execute_command_with_semaphore(msg, "register_tensors", f"batch_{batch_id}", blocking=blocking,
                                                     timeout=timeout)
+        # an older handle of the same batch id no longer owns the registration (the agent replaced it): its close or
+        # garbage collection must not clean up the new one
+        old = self._handlers.get(batch_id)
+        old = old() if old is not None else None
+        if old is not None:
+            old._closed = True
         handler = BatchHandler(self, batch_id, list(dict.fromkeys(pair for _, pair in tensors)))
+        self._handlers[batch_id] = weakref.ref(handler)
         handler._pending = None if blocking else done
         return handler
 

@@ -52,8 +52,6 @@ def _reregister_worker(rank, world, port, tag, tmp):
                 assert batch.query_transfer_signal(timeout=10.0) is False
             if round_no != 1:
                 batch.close()  # round 1 is left open on purpose: registering again replaces it
-            else:
-                batch._closed = True
             dist.barrier()
         assert agent.batches == {} or list(agent.batches) == ["weight_sync"]
     finally:
@@ -249,3 +247,47 @@ def _strided_worker(rank, world, port, tag, tmp):
 
 def test_strided_shard_target_through_the_bus(tmp_path):
     run_distributed(_strided_worker, 6, free_port(), "strided", str(tmp_path))
+
+
+def _abandoned_worker(rank, world, port, tag, tmp):
+    """The receiving worker never asks for the transfer: the send times out with an error, every later transfer of
+    that registration is refused, and registering the batch again works."""
+    import threading
+
+    from etha_b200.kvstore import TorchTCPStore
+    from etha_b200.tensor_bus.agent import TensorBusAgent
+
+    store = TorchTCPStore("127.0.0.1", port, world_size=world, is_master=(rank == 0), timeout=60.0,
+                          wait_for_workers=True, namespace=tag)
+    cq, st = f"{tmp}/{tag}_r{rank}_command.lmdb", f"{tmp}/{tag}_r{rank}_state.lmdb"
+    agent = TensorBusAgent(rank, world, "127.0.0.1", port, cq, st, store_timeout=1.0, store_namespace=tag, store=store,
+                           device="cpu")
+    th = threading.Thread(target=agent.run, daemon=True)
+    th.start()
+    client = TensorBusClient(rank, cq, st, connection_timeout=10.0)
+    try:
+        sender = rank == 0
+        me, other = ("trainer", "inference") if sender else ("inference", "trainer")
+        client.init_pair("w", me, other, 1, torch.tensor([rank]), (Replicate(),), timeout=30.0)
+        t = torch.ones(8) if sender else torch.zeros(8)
+        batch = client.register_tensors("ab", [(t, "w")], timeout=30.0)
+        if sender:
+            with pytest.raises(TensorBusError, match="did not complete within"):
+                batch.transfer("send", blocking=True, timeout=20.0)
+            with pytest.raises(TensorBusError, match="register it again"):
+                batch.transfer("send", blocking=True, timeout=20.0)
+        dist.barrier()
+        # both sides start over under the same batch id; the old handles lose their claim on it
+        batch2 = client.register_tensors("ab", [(t, "w")], timeout=30.0)
+        assert batch._closed
+        del batch
+        batch2.transfer("send" if sender else "recv", blocking=True, timeout=30.0)
+        if not sender:
+            assert torch.equal(t, torch.ones(8))
+        batch2.close()
+    finally:
+        _teardown(agent, th, client)
+
+
+def test_abandoned_transfer_poisons_the_registration_not_the_agent(tmp_path):
+    run_distributed(_abandoned_worker, 2, free_port(), "abandon", str(tmp_path))
