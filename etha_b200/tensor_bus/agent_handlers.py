@@ -175,7 +175,10 @@ class AgentHandlers:
         batch.key = f"batch:{batch_id}/gen:{batch.gen}"
 
         # publish what the other agents need, then wait for theirs
-        meta = {"rank": self.rank, "kind": kind, "local_name": first.local_name, "gen": batch.gen, "host": _hostname()}
+        import uuid
+
+        meta = {"rank": self.rank, "kind": kind, "local_name": first.local_name, "gen": batch.gen, "host": _hostname(),
+                "nonce": uuid.uuid4().hex[:12]}
         if kind == "cuda":
             from ..parallel.peer import PeerMemory
 
@@ -231,7 +234,10 @@ class AgentHandlers:
             # every agent of the batch runs on this machine: the per-transfer rendezvous uses semaphores, not the store
             from .node_barrier import NodeBarrier
 
-            batch.node_barrier = NodeBarrier(f"{self.namespace}/{batch.key}", self.rank, all_ranks)
+            # the scope carries every agent's nonce of this registration: semaphores a crashed earlier run left under the
+            # same namespace and batch id can never be picked up
+            nonces = "".join(metas[r].get("nonce", "") for r in all_ranks)
+            batch.node_barrier = NodeBarrier(f"{self.namespace}/{batch.key}/{nonces}", self.rank, all_ranks)
         if kind == "cuda" and len({m.get("host") for m in metas.values()}) == 1:
             if any(m.get("arena") for m in metas.values()):
                 self._join_multicast_team(batch, metas, all_ranks)
