@@ -65,7 +65,11 @@ class TorchTCPStore(KVStore):
         k = self._prefixed(key, component)
         if not self._store.check([k]):
             return None
-        return self._store.get(k)
+        # `TCPStore.get` would block for the whole store timeout if another process deleted the key between the check
+        # and the read; a compare-and-set that changes nothing returns the current value and never waits (if the key
+        # did vanish, it comes back empty, which every reader here treats as missing)
+        v = self._store.compare_set(k, "", "")
+        return v if v else None
 
     def exists(self, key: str, *, component: str | None = None) -> bool:
         return bool(self._store.check([self._prefixed(key, component)]))

@@ -217,3 +217,27 @@ def test_etcd_waits_sleep_on_a_watch_stream():
             s.wait_for_keys("pair:q/rank:*/t", 1, timeout=0.3)
     finally:
         gw.stop()
+
+
+def test_tcp_get_never_blocks_on_a_key_deleted_under_it():
+    """Another process may delete a key between this store's existence check and its read (a batch cleanup racing
+    with a status query): the read must come back empty at once, not wait for the store timeout."""
+    import time
+
+    s = TorchTCPStore("127.0.0.1", free_port(), world_size=1, is_master=True, timeout=30.0, wait_for_workers=False, namespace="race")
+    s.set("k", "v")
+    assert s.get("k") == b"v"
+    real = s._store
+
+    class CheckSaysYes:
+        def __getattr__(self, name):
+            return getattr(real, name)
+
+        def check(self, keys):
+            return True  # as if the key had existed a moment ago
+
+    s._store = CheckSaysYes()
+    t0 = time.monotonic()
+    assert s.get("gone") is None and s.try_get("gone") is None and s.get_bytes("gone") is None
+    assert time.monotonic() - t0 < 2.0
+    assert s.get("k") == b"v"
