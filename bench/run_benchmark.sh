@@ -12,11 +12,21 @@ launch() { if [ "${N}" = "1" ]; then python "$@"; else ${RUN} --master-port "${P
 
 launch bench.py --gpus "${N}" --impl reference
 launch bench.py --gpus "${N}"
-launch bench/transfer_benchmark.py --config single --max-mb 1024
+launch bench/transfer_benchmark.py --config single --max-mb 4096
+if [ "${N}" -ge 2 ]; then
+  launch bench/transfer_benchmark.py --config single --max-mb 4096 --impl reference   # chunk, 256 MiB buckets, gather-broadcast
+  launch bench.py --gpus "${N}" --model mixtral-8x7b --impl reference
+  launch bench.py --gpus "${N}" --model mixtral-8x7b
+  launch bench.py --gpus "${N}" --source-dtype float32 --impl reference
+  launch bench.py --gpus "${N}" --source-dtype float32
+fi
 if [ "${N}" -ge 4 ]; then
   launch bench/transfer_benchmark.py --config single --max-mb 1024 --layouts "S0->R" --nvls 1
-  launch bench/transfer_benchmark.py --config qwen2-partial
-  launch bench/transfer_benchmark.py --config mixtral
+  launch bench.py --gpus "${N}" --model qwen2-7b --layout partial2x2-tp
+  launch bench.py --gpus "${N}" --model qwen2-7b --layout partial2x2-tp --nvls 1
+fi
+if [ "${N}" = "2" ]; then
+  launch bench/link_bench.py --mb 1024 --iters 20
 fi
 python bench/kernel_bench.py --case all --mb 1024
 python bench/kvstore_benchmark.py --iters 1000
