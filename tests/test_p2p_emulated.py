@@ -198,6 +198,10 @@ TYPED_CASES = [
 
 @pytest.mark.parametrize("case", TYPED_CASES, ids=[str(i) for i in range(len(TYPED_CASES))])
 def test_typed_tables_convert_and_collapse(case, monkeypatch):
+    _check_typed_case(case, monkeypatch)
+
+
+def _check_typed_case(case, monkeypatch):
     ss, sp, ts, tp, shape, sdt, tdt = case
     ns, nt = math.prod(ss), math.prod(ts)
     smesh, tmesh = torch.arange(ns).view(ss), torch.arange(ns, ns + nt).view(ts)
@@ -247,8 +251,13 @@ def test_typed_tables_convert_and_collapse(case, monkeypatch):
         red = [(i, p.reduce_op) for i, p in enumerate(sp) if isinstance(p, Partial)]
         from etha_b200.comm.ir import partial_family
 
-        # the collapse is striped: every member of a family executes part of it
-        assert all(batches[r].table._packed for r in range(ns))
+        # the collapse is striped: every member of a family executes part of it (replica groups that no consumer
+        # reads from, possible when the source also has Replicate dims, stay idle as a whole)
+        if not any(isinstance(p, type(R)) for p in sp):
+            assert all(batches[r].table._packed for r in range(ns))
+        for r in range(ns):
+            fam_ranks = partial_family(smesh, red, r).ranks
+            assert len({bool(batches[q].table._packed) for q in fam_ranks}) == 1, "a family works as a whole or not at all"
         for r in range(ns):
             readers = {p for p in range(ns) if p != r and batches[p].table._packed and r in partial_family(smesh, red, p).ranks}
             assert readers <= set(batches[r]._producers)
@@ -286,3 +295,37 @@ def test_plain_layout_sends_whole_tensors_rank_to_rank(monkeypatch):
             _, dbuf, dbase = world.buffer_of(op.dst[0])
             _emulate(op, sbuf, dbuf, sbase, dbase)
     assert torch.equal(targets[2], sources[0]) and torch.equal(targets[3], sources[1])
+
+
+def test_random_partial_layouts_collapse_to_the_logical_tensor():
+    """Random source meshes with up to two Partial dims, random targets: whatever the merging of per-replica routes
+    and the striping over the family do, every consumer shard must equal the logical (collapsed) tensor."""
+    import random
+
+    rng = random.Random(1234)
+    source_meshes = [(2,), (4,), (2, 2), (2, 3), (3, 2)]
+    target_meshes = [(2,), (3,), (4,), (2, 2)]
+    ops = ["sum", "avg", "max", "min"]
+    seen = 0
+    for _ in range(60):
+        ss, ts = rng.choice(source_meshes), rng.choice(target_meshes)
+        sp = tuple(rng.choice([Shard(0), Shard(1), R, Partial(rng.choice(ops)), Partial(rng.choice(ops))]) for _ in ss)
+        tp = tuple(rng.choice([Shard(0), Shard(1), R]) for _ in ts)
+        if not any(isinstance(p, Partial) for p in sp):
+            continue
+        sdt, tdt = rng.choice([(torch.float32, torch.float32), (torch.float32, torch.bfloat16), (torch.bfloat16, torch.bfloat16)])
+        shape = (rng.choice([12, 24]), rng.choice([12, 36]))  # divisible by 2, 3, 4 and 6
+
+        class Patch:  # the part of pytest's monkeypatch the helper uses
+            def setattr(self, obj, name, value):
+                self.saved = (obj, name, getattr(obj, name))
+                setattr(obj, name, value)
+
+        mp = Patch()
+        try:
+            _check_typed_case((ss, sp, ts, tp, shape, sdt, tdt), mp)
+        finally:
+            obj, name, old = mp.saved
+            setattr(obj, name, old)
+        seen += 1
+    assert seen >= 30

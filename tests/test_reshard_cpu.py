@@ -55,10 +55,15 @@ def _make_source_local(rank, smesh, splc, shape, dtype, slice_view):
     full = torch.randn(shape, generator=g).to(dtype)
     if not has_partial:
         return full, None
-    # every rank of a family holds an independent random value of the family's shard
+    # every rank of a family holds an independent random value of the family's shard; ranks that differ only along a
+    # Replicate mesh dim hold the same value (that is what Replicate means), so the seed ignores those coordinates
     contribs = {}
     for r in smesh.reshape(-1).tolist():
-        gr = torch.Generator().manual_seed(1000 + r)
+        coord = (smesh == r).nonzero()[0].tolist()
+        key = 0
+        for c, size, p in zip(coord, smesh.shape, splc):
+            key = key * int(size) + (0 if isinstance(p, Replicate) else int(c))
+        gr = torch.Generator().manual_seed(1000 + key)
         contribs[r] = torch.randn(local_slice_of(full, smesh, eff, r).shape, generator=gr).to(dtype)
     reductions = [(i, p.reduce_op) for i, p in enumerate(splc) if isinstance(p, Partial)]
     logical = torch.zeros(shape, dtype=dtype)
