@@ -83,6 +83,10 @@ CASES = [
 @pytest.mark.parametrize("overlap", [False, True])
 @pytest.mark.parametrize("case", CASES, ids=[str(i) for i in range(len(CASES))])
 def test_tables_of_all_ranks_deliver_every_shard(case, overlap, monkeypatch):
+    _check_copy_case(case, overlap, monkeypatch)
+
+
+def _check_copy_case(case, overlap, monkeypatch):
     ss, sp, ts, tp, shape = case
     ns, nt = math.prod(ss), math.prod(ts)
     smesh = torch.arange(ns).view(ss)
@@ -329,3 +333,31 @@ def test_random_partial_layouts_collapse_to_the_logical_tensor():
             setattr(obj, name, old)
         seen += 1
     assert seen >= 30
+
+
+def test_random_copy_layouts_deliver_every_shard():
+    """Random meshes, placements and (often unevenly divisible) shapes, disjoint and overlapping rank sets."""
+    import random
+
+    rng = random.Random(99)
+    meshes = [(1,), (2,), (3,), (4,), (2, 2), (2, 3), (1, 2, 2)]
+    for _ in range(40):
+        ss, ts = rng.choice(meshes), rng.choice(meshes)
+        sp = tuple(rng.choice([Shard(0), Shard(1), R]) for _ in ss)
+        tp = tuple(rng.choice([Shard(0), Shard(1), R]) for _ in ts)
+        shape = (rng.choice([7, 12, 16, 30]), rng.choice([5, 12, 64]))
+        overlap = rng.random() < 0.4
+
+        class Patch:
+            def setattr(self, obj, name, value):
+                self.saved = (obj, name, getattr(obj, name))
+                setattr(obj, name, value)
+
+        mp = Patch()
+        try:
+            _check_copy_case((ss, sp, ts, tp, shape), overlap, mp)
+        except Exception as e:
+            raise AssertionError(f"{(ss, sp, ts, tp, shape, overlap)}: {type(e).__name__}: {e}") from e
+        finally:
+            obj, name, old = mp.saved
+            setattr(obj, name, old)
